@@ -24,17 +24,19 @@ int lbk_kv_gather(const void* ring, const void* first, const void* knew, const v
 int lbk_masked_attention(const void* q, long ldq, const void* kbase, const void* vbase, long ldkv, const void* ring, const void* first,
                          int L, int nfirst, const int* ext_off, const int* nsink, const int* cstart, const int* slots,
                          const void* gate, long ldg, const int* tok_seq, const int* seq_off, const int* past, void* y, long ldy,
-                         long tokens, int H, int G, int D, int V, int window, int chunk, int keep, float scale, int dtype,
-                         cudaStream_t s);
+                         long tokens, int H, int G, int D, int V, int window, int chunk, int keep, float scale, float softcap,
+                         int sink, int gate_wide, float out_scale, int dtype, cudaStream_t s);
 int lbk_masked_attention_mma(const void* q, long ldq, const void* kbase, const void* vbase, long ldkv, const int* ext_off,
                              const int* nsink, const int* cstart, const void* gate, long ldg, const int* qt_seq, const int* qt_start,
                              int n_qtiles, const int* seq_off, const int* past, void* y, long ldy, int H, int G, int D, int V,
-                             int window, int chunk, int keep, float scale, cudaStream_t s);
+                             int window, int chunk, int keep, float scale, float softcap, int sink, int gate_wide, float out_scale,
+                             cudaStream_t s);
 int lbk_ring_decode(const void* q, long ldq, const void* ring, const void* first, int L, int nfirst, const int* slots, const int* past,
                     const void* gate, long ldg, void* y, long ldy, float* part, int B, int H, int G, int D, int V, int window,
-                    int chunk, int keep, float scale, int splits, int dtype, cudaStream_t s);
-int lbk_moe_topk(const float* z, long ldz, int E, int top, float rscale, int* idx, float* wts, int* counts, long tokens,
-                 cudaStream_t s);
+                    int chunk, int keep, float scale, int splits, float softcap, int sink, int gate_wide, float out_scale, int dtype,
+                    cudaStream_t s);
+int lbk_moe_topk(const float* z, long ldz, const float* bias, int mode, int E, int top, float rscale, int* idx, float* wts, int* counts,
+                 long tokens, cudaStream_t s);
 int lbk_moe_pairs(const void* h, long ldh, const void* wgu, const void* wd, const int* idx, const float* wts, void* a, float* out,
                   long tokens, int ff, int n, int top, int act, int dtype, cudaStream_t s);
 int lbk_moe_sort(const void* h, long ldh, const int* idx, const int* counts, int* offsets, int* cursor, int* pos, void* xs, long tokens,
@@ -180,63 +182,69 @@ void kv_gather(const Tensor& ring, const Tensor& first, const Tensor& knew, cons
 void masked_attention(const Tensor& q, const Tensor& kmat, const Tensor& vmat, const Tensor& ext_off, const Tensor& nsink,
                       const Tensor& cstart, const OptT& gate, const Tensor& tok_seq, const Tensor& seq_off, const Tensor& past,
                       const OptT& qt_seq, const OptT& qt_start, Tensor y, int64_t H, int64_t G, int64_t D, int64_t V, int64_t window,
-                      int64_t chunk, int64_t keep, double scale) {
+                      int64_t chunk, int64_t keep, double scale, double softcap, bool sink, bool gate_wide, double out_scale) {
   rows2d(q, "masked_attention q"); rows2d(kmat, "masked_attention k"); rows2d(vmat, "masked_attention v"); rows2d(y, "masked_attention y");
   const int dtype = code(q);
   TORCH_CHECK(q.size(1) == H * D && kmat.size(1) == G * D && vmat.size(1) == G * V && y.size(1) == H * V && y.size(0) == q.size(0) &&
               kmat.stride(0) == vmat.stride(0) && code(kmat) == dtype && code(vmat) == dtype && code(y) == dtype, "masked_attention: shapes");
   long ldg = 0;
-  if (has(gate)) { rows2d(*gate, "masked_attention gate"); TORCH_CHECK(gate->size(1) == H && code(*gate) == dtype, "masked_attention: gate [tokens, H]"); ldg = gate->stride(0); }
+  if (has(gate)) { rows2d(*gate, "masked_attention gate"); TORCH_CHECK(gate->size(1) == (gate_wide ? H * V : H) && code(*gate) == dtype, "masked_attention: gate [tokens, H] (or [tokens, H V])"); ldg = gate->stride(0); }
   c10::cuda::CUDAGuard guard(q.device());
   if (has(qt_seq)) {
     TORCH_CHECK(dtype == 1 && has(qt_start), "masked_attention: the tensor-core kernel takes bf16");
     check(lbk_masked_attention_mma(q.data_ptr(), q.stride(0), kmat.data_ptr(), vmat.data_ptr(), kmat.stride(0), meta(ext_off), meta(nsink),
                                    meta(cstart), ptr_opt(gate), ldg, meta(*qt_seq), meta(*qt_start), (int)qt_seq->numel(), meta(seq_off),
                                    meta(past), y.data_ptr(), y.stride(0), (int)H, (int)G, (int)D, (int)V, (int)window, (int)chunk, (int)keep,
-                                   (float)scale, cur_stream()), "masked_attention (tensor cores)");
+                                   (float)scale, (float)softcap, (int)sink, (int)gate_wide, (float)out_scale, cur_stream()),
+          "masked_attention (tensor cores)");
     return;
   }
   check(lbk_masked_attention(q.data_ptr(), q.stride(0), kmat.data_ptr(), vmat.data_ptr(), kmat.stride(0), nullptr, nullptr, 0, 0,
                              meta(ext_off), meta(nsink), meta(cstart), nullptr, ptr_opt(gate), ldg, meta(tok_seq), meta(seq_off), meta(past),
                              y.data_ptr(), y.stride(0), q.size(0), (int)H, (int)G, (int)D, (int)V, (int)window, (int)chunk, (int)keep,
-                             (float)scale, dtype, cur_stream()), "masked_attention");
+                             (float)scale, (float)softcap, (int)sink, (int)gate_wide, (float)out_scale, dtype, cur_stream()), "masked_attention");
 }
 
 // single-token steps: keys / values straight from the ring and the kept-first rows.  splits == 0: one warp per (token, head);
 // splits > 0: the grouped kernel, the keys of a (sequence, key head) cut into `splits` parts and merged.
 void ring_attention(const Tensor& q, const Tensor& ring, const Tensor& first, const OptT& gate, const Tensor& tok_seq, const Tensor& seq_off,
                     const Tensor& slots, const Tensor& past, Tensor y, int64_t H, int64_t G, int64_t D, int64_t V, int64_t window,
-                    int64_t chunk, int64_t keep, double scale, int64_t splits) {
+                    int64_t chunk, int64_t keep, double scale, int64_t splits, double softcap, bool sink, bool gate_wide, double out_scale) {
   rows2d(q, "ring_attention q"); rows2d(y, "ring_attention y");
   const int dtype = code(q);
   ring_shapes(ring, first, G * (D + V));
   TORCH_CHECK(q.size(1) == H * D && y.size(1) == H * V && y.size(0) == q.size(0) && code(ring) == dtype && code(y) == dtype &&
               q.size(0) == slots.numel(), "ring_attention: shapes (one token per sequence)");
   long ldg = 0;
-  if (has(gate)) { rows2d(*gate, "ring_attention gate"); TORCH_CHECK(gate->size(1) == H && code(*gate) == dtype, "ring_attention: gate [tokens, H]"); ldg = gate->stride(0); }
+  if (has(gate)) { rows2d(*gate, "ring_attention gate"); TORCH_CHECK(gate->size(1) == (gate_wide ? H * V : H) && code(*gate) == dtype, "ring_attention: gate [tokens, H] (or [tokens, H V])"); ldg = gate->stride(0); }
   c10::cuda::CUDAGuard guard(q.device());
   if (splits > 0) {
     Tensor part = at::empty({q.size(0) * H * splits * (V + 2)}, q.options().dtype(at::kFloat));
     check(lbk_ring_decode(q.data_ptr(), q.stride(0), ring.data_ptr(), first.data_ptr(), (int)ring.size(1), (int)first.size(1), meta(slots),
                           meta(past), ptr_opt(gate), ldg, y.data_ptr(), y.stride(0), part.data_ptr<float>(), (int)q.size(0), (int)H, (int)G,
-                          (int)D, (int)V, (int)window, (int)chunk, (int)keep, (float)scale, (int)splits, dtype, cur_stream()), "ring_decode");
+                          (int)D, (int)V, (int)window, (int)chunk, (int)keep, (float)scale, (int)splits, (float)softcap, (int)sink, (int)gate_wide,
+                          (float)out_scale, dtype, cur_stream()), "ring_decode");
     return;
   }
   check(lbk_masked_attention(q.data_ptr(), q.stride(0), nullptr, nullptr, 0, ring.data_ptr(), first.data_ptr(), (int)ring.size(1),
                              (int)first.size(1), nullptr, nullptr, nullptr, meta(slots), ptr_opt(gate), ldg, meta(tok_seq), meta(seq_off),
                              meta(past), y.data_ptr(), y.stride(0), q.size(0), (int)H, (int)G, (int)D, (int)V, (int)window, (int)chunk,
-                             (int)keep, (float)scale, dtype, cur_stream()), "ring_attention");
+                             (int)keep, (float)scale, (float)softcap, (int)sink, (int)gate_wide, (float)out_scale, dtype, cur_stream()),
+        "ring_attention");
 }
 
-void moe_topk(const Tensor& z, int64_t top, double rscale, Tensor idx, Tensor wts, const OptT& counts) {
+void moe_topk(const Tensor& z, const OptT& bias, int64_t mode, int64_t top, double rscale, Tensor idx, Tensor wts, const OptT& counts) {
   rows2d(z, "moe_topk z");
   TORCH_CHECK(z.scalar_type() == at::kFloat, "moe_topk: fp32 router logits expected");
   TORCH_CHECK(idx.is_cuda() && idx.scalar_type() == at::kInt && idx.is_contiguous() && idx.numel() == z.size(0) * top, "moe_topk: idx int32 [tokens, top]");
   TORCH_CHECK(wts.is_cuda() && wts.scalar_type() == at::kFloat && wts.is_contiguous() && wts.numel() == z.size(0) * top, "moe_topk: weights fp32 [tokens, top]");
+  const float* bp = nullptr;
+  if (has(bias)) { TORCH_CHECK(bias->is_cuda() && bias->scalar_type() == at::kFloat && bias->is_contiguous() && bias->numel() == z.size(1), "moe_topk: bias fp32 [E]"); bp = bias->data_ptr<float>(); }
+  TORCH_CHECK(mode == 0 || mode == 1, "moe_topk: mode 0 (sigmoid scores) or 1 (softmax over the chosen logits)");
   int* cp = nullptr;
   if (has(counts)) { TORCH_CHECK(counts->is_cuda() && counts->scalar_type() == at::kInt && counts->numel() >= z.size(1), "moe_topk: counts"); cp = counts->data_ptr<int>(); }
   c10::cuda::CUDAGuard guard(z.device());
-  check(lbk_moe_topk(z.data_ptr<float>(), z.stride(0), (int)z.size(1), (int)top, (float)rscale, idx.data_ptr<int>(), wts.data_ptr<float>(), cp,
+  check(lbk_moe_topk(z.data_ptr<float>(), z.stride(0), bp, (int)mode, (int)z.size(1), (int)top, (float)rscale, idx.data_ptr<int>(), wts.data_ptr<float>(), cp,
                      z.size(0), cur_stream()), "moe_topk");
 }
 
@@ -283,9 +291,9 @@ TORCH_LIBRARY(libai_b200_kv, m) {
   m.def("qk_prepare(Tensor(a!) q, Tensor(b!)? k, Tensor? qw, Tensor? kw, Tensor freq, float mscale, int H, int G, int D, float eps, bool full_norm, bool unit_norm, Tensor tok_seq, Tensor seq_off, Tensor past) -> ()", &qk_prepare);
   m.def("kv_write(Tensor(a!) ring, Tensor(b!) first, Tensor knew, Tensor vnew, Tensor tok_seq, Tensor seq_off, Tensor slots, Tensor past) -> ()", &kv_write);
   m.def("kv_gather(Tensor ring, Tensor first, Tensor knew, Tensor vnew, Tensor ext_seq, Tensor ext_off, Tensor nsink, Tensor cstart, Tensor seq_off, Tensor slots, Tensor past, Tensor(a!) ext) -> ()", &kv_gather);
-  m.def("masked_attention(Tensor q, Tensor kmat, Tensor vmat, Tensor ext_off, Tensor nsink, Tensor cstart, Tensor? gate, Tensor tok_seq, Tensor seq_off, Tensor past, Tensor? qt_seq, Tensor? qt_start, Tensor(a!) y, int H, int G, int D, int V, int window, int chunk, int keep, float scale) -> ()", &masked_attention);
-  m.def("ring_attention(Tensor q, Tensor ring, Tensor first, Tensor? gate, Tensor tok_seq, Tensor seq_off, Tensor slots, Tensor past, Tensor(a!) y, int H, int G, int D, int V, int window, int chunk, int keep, float scale, int splits) -> ()", &ring_attention);
-  m.def("moe_topk(Tensor z, int top, float rscale, Tensor(a!) idx, Tensor(b!) wts, Tensor(c!)? counts) -> ()", &moe_topk);
+  m.def("masked_attention(Tensor q, Tensor kmat, Tensor vmat, Tensor ext_off, Tensor nsink, Tensor cstart, Tensor? gate, Tensor tok_seq, Tensor seq_off, Tensor past, Tensor? qt_seq, Tensor? qt_start, Tensor(a!) y, int H, int G, int D, int V, int window, int chunk, int keep, float scale, float softcap=0.0, bool sink=False, bool gate_wide=False, float out_scale=1.0) -> ()", &masked_attention);
+  m.def("ring_attention(Tensor q, Tensor ring, Tensor first, Tensor? gate, Tensor tok_seq, Tensor seq_off, Tensor slots, Tensor past, Tensor(a!) y, int H, int G, int D, int V, int window, int chunk, int keep, float scale, int splits, float softcap=0.0, bool sink=False, bool gate_wide=False, float out_scale=1.0) -> ()", &ring_attention);
+  m.def("moe_topk(Tensor z, Tensor? bias, int mode, int top, float rscale, Tensor(a!) idx, Tensor(b!) wts, Tensor(c!)? counts) -> ()", &moe_topk);
   m.def("moe_pairs(Tensor h, Tensor wgu, Tensor wd, Tensor idx, Tensor wts, Tensor(a!) a, Tensor(b!) out, int act) -> ()", &moe_pairs);
   m.def("moe_sort(Tensor h, Tensor idx, Tensor counts, Tensor(a!) offsets, Tensor(b!) cursor, Tensor(c!) pos, Tensor(d!) xs, int align, Tensor(e!)? tile_group) -> ()", &moe_sort);
 }

@@ -386,7 +386,13 @@ __global__ void kv_gather_kernel(const T* __restrict__ ring, const T* __restrict
 // for the scores and value channels for the output; softmax in fp32, streamed 32 keys at a time.  The head's output is
 // multiplied by sigmoid(gate[tok, h]) when a gate is given.  Keys come from the ext matrix (kbase/vbase with row stride
 // ldkv) or, when `ring` is given, from ring / first (single-token steps).
+//
+// Options of every attention kernel of this file (AttnExtra): `softcap` > 0 passes the scaled scores through
+// cap * tanh(score / cap); `sink` adds one entry of score 0 without a value to the softmax (its denominator grows by
+// exp(0)); `gate_wide` reads one gate logit per output channel (gate[tok, h*V + c]) instead of one per head; the result
+// is multiplied by `out_scale`.
 // ------------------------------------------------------------------------------------------------------------------
+struct AttnExtra { float softcap, out_scale; int sink, gate_wide; };
 constexpr int ATT_MAXV = 8;    // value channels per lane: V <= 256
 
 struct KvSource {
@@ -412,7 +418,7 @@ template <typename T>
 __global__ void masked_attention_kernel(const T* __restrict__ q, long ldq, KvSource src, const T* __restrict__ gate, long ldg,
                                         const int* __restrict__ tok_seq, const int* __restrict__ seq_off, const int* __restrict__ past,
                                         T* __restrict__ y, long ldy, long tokens, int H, int G, int D, int V, int window, int chunk,
-                                        int keep, float scale) {
+                                        int keep, float scale, AttnExtra ex) {
   extern __shared__ float sm[];
   const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long wid = (long)blockIdx.x * (blockDim.x >> 5) + wib;
@@ -439,7 +445,7 @@ __global__ void masked_attention_kernel(const T* __restrict__ q, long ldq, KvSou
       kv_row<T>(src, b, mine < nA ? mine : lo + mine - nA, g, D, V, kp, vp);
       float d = 0.f;
       for (int i = 0; i < D; ++i) d += qs[i] * ldf(kp + i);
-      sc = d;
+      sc = ex.softcap > 0.f ? ex.softcap * tanhf(d / ex.softcap) : d;
     }
     const float mn = fmaxf(m, warp_max(sc));
     const float corr = expf(m - mn);             // m = -inf on the first block: exp(-inf) = 0
@@ -456,10 +462,17 @@ __global__ void masked_attention_kernel(const T* __restrict__ q, long ldq, KvSou
     }
     m = mn;
   }
-  const float gt = gate ? sigmoidf_(ldf(gate + tok * ldg + h)) : 1.f;
-  const float inv = gt / l;
+  if (ex.sink) l += expf(-m);                    // the entry of score 0 (m is finite: a query sees itself)
+  const float gt = (gate && !ex.gate_wide) ? sigmoidf_(ldf(gate + tok * ldg + h)) : 1.f;
+  const float inv = gt * ex.out_scale / l;
 #pragma unroll
-  for (int i = 0; i < ATT_MAXV; ++i) { const int c = lane + 32 * i; if (c < V) stf(y + tok * ldy + h * V + c, acc[i] * inv); }
+  for (int i = 0; i < ATT_MAXV; ++i) {
+    const int c = lane + 32 * i;
+    if (c < V) {
+      const float gw = (gate && ex.gate_wide) ? sigmoidf_(ldf(gate + tok * ldg + h * V + c)) : 1.f;
+      stf(y + tok * ldy + h * V + c, acc[i] * inv * gw);
+    }
+  }
 }
 
 // ------------------------------------------------------------------------------------------------------------------
@@ -479,6 +492,10 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
+// cap * tanh(s / cap) for the tensor-core kernel: tanh(x) = 1 - 2 / (exp(2x) + 1), absolute error of a few 1e-7
+__device__ __forceinline__ float soft_capped(float s, float cap, float inv_cap) {
+  return cap * (1.f - __fdividef(2.f, __expf(2.f * s * inv_cap) + 1.f));
+}
 __device__ __forceinline__ int mask_floor(int p, int window, int chunk) {
   return chunk > 0 ? (p / chunk) * chunk : (window > 0 ? max(0, p - window + 1) : 0);
 }
@@ -490,7 +507,7 @@ masked_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long ldq, const
                             const int* __restrict__ nsink, const int* __restrict__ cstart, const __nv_bfloat16* __restrict__ gate, long ldg,
                             const int* __restrict__ qt_seq, const int* __restrict__ qt_start, const int* __restrict__ seq_off,
                             const int* __restrict__ past, __nv_bfloat16* __restrict__ y, long ldy, int H, int G, int window, int chunk,
-                            int keep, float scale) {
+                            int keep, float scale, AttnExtra ex) {
   constexpr int KT = 64, KS = D + 8, VS = V + 8, BUF = KT * (KS + VS);
   extern __shared__ __align__(16) unsigned char mma_smem[];              // two buffers of [K tile | V tile]
   __nv_bfloat16* const tiles = reinterpret_cast<__nv_bfloat16*>(mma_smem);
@@ -583,6 +600,8 @@ masked_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long ldq, const
         mma_bf16(sacc[j + 1], qf[kk], b2, b3);
       }
     }
+    const bool capped = ex.softcap > 0.f;
+    const float inv_cap = capped ? 1.f / ex.softcap : 0.f;
     float mx0 = -INFINITY, mx1 = -INFINITY;
     // a tile that every query of the warp sees completely needs no mask (warp-uniform)
     const bool whole = phaseA ? (k0 + KT <= rlim)
@@ -592,7 +611,8 @@ masked_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long ldq, const
       for (int j = 0; j < 8; ++j) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          const float sv = sacc[j][c] * scale;
+          float sv = sacc[j][c] * scale;
+          if (capped) sv = soft_capped(sv, ex.softcap, inv_cap);
           sacc[j][c] = sv;
           if (c < 2) mx0 = fmaxf(mx0, sv); else mx1 = fmaxf(mx1, sv);
         }
@@ -606,7 +626,9 @@ masked_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long ldq, const
           const int pj = row < ns ? row : cs + row - ns;
           const int pi = c < 2 ? pi0 : pi1, lo = c < 2 ? lo0 : lo1;
           const bool valid = row < rlim && pj <= pi && (phaseA || pj >= lo || pj < keep);
-          const float sv = valid ? sacc[j][c] * scale : -INFINITY;
+          float sv = sacc[j][c] * scale;
+          if (capped) sv = soft_capped(sv, ex.softcap, inv_cap);
+          if (!valid) sv = -INFINITY;
           sacc[j][c] = sv;
           if (c < 2) mx0 = fmaxf(mx0, sv); else mx1 = fmaxf(mx1, sv);
         }
@@ -654,14 +676,27 @@ masked_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long ldq, const
   }
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-  const float g0 = (gate && r0 < n) ? sigmoidf_(__bfloat162float(gate[(tokbase + r0) * ldg + h])) : 1.f;
-  const float g1 = (gate && r1 < n) ? sigmoidf_(__bfloat162float(gate[(tokbase + r1) * ldg + h])) : 1.f;
-  const float i0 = g0 / l0, i1 = g1 / l1;
+  if (ex.sink) { l0 += __expf(-m0); l1 += __expf(-m1); }                // the entry of score 0 (rows beyond n: 0 / inf = 0, never stored)
+  const bool narrow = gate && !ex.gate_wide, wide = gate && ex.gate_wide;
+  const float g0 = (narrow && r0 < n) ? sigmoidf_(__bfloat162float(gate[(tokbase + r0) * ldg + h])) : 1.f;
+  const float g1 = (narrow && r1 < n) ? sigmoidf_(__bfloat162float(gate[(tokbase + r1) * ldg + h])) : 1.f;
+  const float i0 = g0 * ex.out_scale / l0, i1 = g1 * ex.out_scale / l1;
 #pragma unroll
   for (int j = 0; j < V / 8; ++j) {
     const int col = h * V + j * 8 + tig * 2;
-    if (r0 < n) *reinterpret_cast<uint32_t*>(y + (tokbase + r0) * ldy + col) = pack_bf16(o[j][0] * i0, o[j][1] * i0);
-    if (r1 < n) *reinterpret_cast<uint32_t*>(y + (tokbase + r1) * ldy + col) = pack_bf16(o[j][2] * i1, o[j][3] * i1);
+    float a0 = o[j][0] * i0, a1 = o[j][1] * i0, b0 = o[j][2] * i1, b1 = o[j][3] * i1;
+    if (wide) {
+      if (r0 < n) {
+        const __nv_bfloat162 gg = *reinterpret_cast<const __nv_bfloat162*>(gate + (tokbase + r0) * ldg + col);
+        a0 *= sigmoidf_(__low2float(gg)); a1 *= sigmoidf_(__high2float(gg));
+      }
+      if (r1 < n) {
+        const __nv_bfloat162 gg = *reinterpret_cast<const __nv_bfloat162*>(gate + (tokbase + r1) * ldg + col);
+        b0 *= sigmoidf_(__low2float(gg)); b1 *= sigmoidf_(__high2float(gg));
+      }
+    }
+    if (r0 < n) *reinterpret_cast<uint32_t*>(y + (tokbase + r0) * ldy + col) = pack_bf16(a0, a1);
+    if (r1 < n) *reinterpret_cast<uint32_t*>(y + (tokbase + r1) * ldy + col) = pack_bf16(b0, b1);
   }
 }
 
@@ -694,7 +729,7 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 ring_decode_kernel(const T* __restrict__ q, long ldq, const T* __restrict__ ring, const T* __restrict__ first, int L, int nfirst,
                    const int* __restrict__ slots, const int* __restrict__ past, float* __restrict__ part, int H, int G, int D, int V,
-                   int window, int chunk, int keep, float scale, int splits, int vec) {
+                   int window, int chunk, int keep, float scale, int splits, int vec, float softcap) {
   extern __shared__ float sm[];
   const int b = blockIdx.x, g = blockIdx.y, sp = blockIdx.z;
   const int R = H / G, C = G * (D + V), KC = G * D;
@@ -751,7 +786,10 @@ ring_decode_kernel(const T* __restrict__ q, long ldq, const T* __restrict__ ring
         }
       }
 #pragma unroll
-      for (int r = 0; r < DEC_MAXR; ++r) if (r >= R) sc[r] = -INFINITY;
+      for (int r = 0; r < DEC_MAXR; ++r) {
+        if (r >= R) sc[r] = -INFINITY;
+        else if (softcap > 0.f) sc[r] = softcap * tanhf(sc[r] / softcap);
+      }
     }
     float p[DEC_MAXR];
 #pragma unroll
@@ -813,18 +851,20 @@ ring_decode_kernel(const T* __restrict__ q, long ldq, const T* __restrict__ ring
 
 template <typename T>
 __global__ void ring_decode_merge_kernel(const float* __restrict__ part, const T* __restrict__ gate, long ldg, T* __restrict__ y, long ldy,
-                                         int H, int V, int splits) {
+                                         int H, int V, int splits, AttnExtra ex) {
   const int b = blockIdx.x, h = blockIdx.y, W = V + 2;
   const float* src = part + ((long)b * H + h) * splits * W;
   float mm = -INFINITY;
   for (int s = 0; s < splits; ++s) mm = fmaxf(mm, src[s * W]);
   float ll = 0.f;
   for (int s = 0; s < splits; ++s) ll += src[s * W] == -INFINITY ? 0.f : src[s * W + 1] * expf(src[s * W] - mm);
-  const float gt = gate ? sigmoidf_(ldf(gate + (long)b * ldg + h)) : 1.f;
+  if (ex.sink) ll += expf(-mm);                  // the entry of score 0
+  const float gt = (gate && !ex.gate_wide) ? sigmoidf_(ldf(gate + (long)b * ldg + h)) : 1.f;
   for (int ch = threadIdx.x; ch < V; ch += blockDim.x) {
     float a = 0.f;
     for (int s = 0; s < splits; ++s) a += src[s * W] == -INFINITY ? 0.f : src[s * W + 2 + ch] * expf(src[s * W] - mm);
-    stf(y + (long)b * ldy + h * V + ch, a * gt / ll);
+    const float gw = (gate && ex.gate_wide) ? sigmoidf_(ldf(gate + (long)b * ldg + h * V + ch)) : 1.f;
+    stf(y + (long)b * ldy + h * V + ch, a * (gt * ex.out_scale) / ll * gw);
   }
 }
 
@@ -838,19 +878,23 @@ __global__ void ring_decode_merge_kernel(const float* __restrict__ part, const T
 //                 run as dense products on their row ranges, and the fused residual kernel gathers the weighted sum.
 // Expert matrices are stacked: wgu [E, 2*ff, n] (gate rows, then up rows), wd [E, n, ff].
 // ------------------------------------------------------------------------------------------------------------------
-// one warp per token over its fp32 router logits z [tokens, E]
-__global__ void moe_topk_kernel(const float* __restrict__ z, long ldz, int E, int top, float rscale, int* __restrict__ idx,
-                                float* __restrict__ wts, int* __restrict__ counts, long tokens) {
+// one warp per token over its fp32 router logits z [tokens, E] (+ bias [E] when given).  mode 0: scores sigmoid(z), weights
+// score / (sum of the chosen scores + 1e-20) * rscale; mode 1: scores z, weights = softmax over the chosen logits, times rscale
+__global__ void moe_topk_kernel(const float* __restrict__ z, long ldz, const float* __restrict__ bias, int mode, int E, int top,
+                                float rscale, int* __restrict__ idx, float* __restrict__ wts, int* __restrict__ counts, long tokens) {
   extern __shared__ float sm[];
   const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const long tok = (long)blockIdx.x * nw + wib;
   float* sc = sm + (long)wib * E;
   if (tok >= tokens) return;                     // warps are independent below
-  for (int e = lane; e < E; e += 32) sc[e] = sigmoidf_(z[tok * ldz + e]);
+  for (int e = lane; e < E; e += 32) {
+    const float v = z[tok * ldz + e] + (bias ? bias[e] : 0.f);
+    sc[e] = mode == 0 ? sigmoidf_(v) : v;
+  }
   __syncwarp();
-  float sum = 0.f, mine_w = 0.f; int mine_e = 0;
+  float sum = 0.f, mine_w = 0.f, first = 0.f; int mine_e = 0;
   for (int k = 0; k < top; ++k) {
-    float best = -1.f; int be = 0x7fffffff;
+    float best = -INFINITY; int be = 0x7fffffff;
     for (int e = lane; e < E; e += 32) { const float v = sc[e]; if (v > best) { best = v; be = e; } }
 #pragma unroll
     for (int mk = 16; mk > 0; mk >>= 1) {
@@ -858,9 +902,11 @@ __global__ void moe_topk_kernel(const float* __restrict__ z, long ldz, int E, in
       const int oe = __shfl_xor_sync(0xffffffffu, be, mk);
       if (ov > best || (ov == best && oe < be)) { best = ov; be = oe; }
     }
-    sum += best;
-    if (lane == k % 32) { mine_w = best; mine_e = be; }
-    if (lane == 0) sc[be] = -2.f;
+    if (k == 0) first = best;
+    const float wk = mode == 0 ? best : expf(best - first);   // the first choice is the largest logit
+    sum += wk;
+    if (lane == k % 32) { mine_w = wk; mine_e = be; }
+    if (lane == 0) sc[be] = -INFINITY;
     __syncwarp();
     if (k % 32 == 31 || k == top - 1) {          // flush up to 32 choices held one per lane
       const int k0 = k - (k % 32);
@@ -868,7 +914,7 @@ __global__ void moe_topk_kernel(const float* __restrict__ z, long ldz, int E, in
     }
   }
   __syncwarp();
-  const float inv = rscale / (sum + 1e-20f);
+  const float inv = rscale / (mode == 0 ? sum + 1e-20f : sum);
   for (int k = lane; k < top; k += 32) {
     wts[tok * top + k] *= inv;
     if (counts) atomicAdd(counts + idx[tok * top + k], 1);
@@ -1065,9 +1111,10 @@ int lbk_kv_gather(const void* ring, const void* first, const void* knew, const v
 int lbk_masked_attention(const void* q, long ldq, const void* kbase, const void* vbase, long ldkv, const void* ring, const void* first,
                          int L, int nfirst, const int* ext_off, const int* nsink, const int* cstart, const int* slots,
                          const void* gate, long ldg, const int* tok_seq, const int* seq_off, const int* past, void* y, long ldy,
-                         long tokens, int H, int G, int D, int V, int window, int chunk, int keep, float scale, int dtype,
-                         cudaStream_t s) {
+                         long tokens, int H, int G, int D, int V, int window, int chunk, int keep, float scale, float softcap,
+                         int sink, int gate_wide, float out_scale, int dtype, cudaStream_t s) {
   if (tokens == 0) return 0;
+  const AttnExtra ex{softcap, out_scale, sink, gate_wide};
   if (V > 32 * ATT_MAXV || G <= 0 || H % G) return -1;
   KvSource src{kbase, vbase, ldkv, ring, first, L, nfirst, G * (D + V), G * D, ext_off, nsink, cstart, slots};
   const int warps = 4;
@@ -1075,18 +1122,18 @@ int lbk_masked_attention(const void* q, long ldq, const void* kbase, const void*
   const unsigned grid = (unsigned)((nwarps + warps - 1) / warps);
   const size_t smem = (size_t)warps * D * sizeof(float);
   if (dtype) masked_attention_kernel<bf16><<<grid, warps * 32, smem, s>>>((const bf16*)q, ldq, src, (const bf16*)gate, ldg, tok_seq,
-      seq_off, past, (bf16*)y, ldy, tokens, H, G, D, V, window, chunk, keep, scale);
+      seq_off, past, (bf16*)y, ldy, tokens, H, G, D, V, window, chunk, keep, scale, ex);
   else masked_attention_kernel<float><<<grid, warps * 32, smem, s>>>((const float*)q, ldq, src, (const float*)gate, ldg, tok_seq,
-      seq_off, past, (float*)y, ldy, tokens, H, G, D, V, window, chunk, keep, scale);
+      seq_off, past, (float*)y, ldy, tokens, H, G, D, V, window, chunk, keep, scale, ex);
   LAUNCH_END();
 }
 
-int lbk_moe_topk(const float* z, long ldz, int E, int top, float rscale, int* idx, float* wts, int* counts, long tokens,
-                 cudaStream_t s) {
+int lbk_moe_topk(const float* z, long ldz, const float* bias, int mode, int E, int top, float rscale, int* idx, float* wts, int* counts,
+                 long tokens, cudaStream_t s) {
   if (tokens == 0) return 0;
   if (top > E || (size_t)E * sizeof(float) > 12 * 1024) return -1;
   const int warps = 4;
-  moe_topk_kernel<<<(unsigned)((tokens + warps - 1) / warps), warps * 32, (size_t)warps * E * sizeof(float), s>>>(z, ldz, E, top, rscale,
+  moe_topk_kernel<<<(unsigned)((tokens + warps - 1) / warps), warps * 32, (size_t)warps * E * sizeof(float), s>>>(z, ldz, bias, mode, E, top, rscale,
                                                                                                                idx, wts, counts, tokens);
   LAUNCH_END();
 }
@@ -1128,9 +1175,11 @@ int lbk_moe_sort(const void* h, long ldh, const int* idx, const int* counts, int
 int lbk_masked_attention_mma(const void* q, long ldq, const void* kbase, const void* vbase, long ldkv, const int* ext_off,
                              const int* nsink, const int* cstart, const void* gate, long ldg, const int* qt_seq, const int* qt_start,
                              int n_qtiles, const int* seq_off, const int* past, void* y, long ldy, int H, int G, int D, int V,
-                             int window, int chunk, int keep, float scale, cudaStream_t s) {
+                             int window, int chunk, int keep, float scale, float softcap, int sink, int gate_wide, float out_scale,
+                             cudaStream_t s) {
   if (n_qtiles == 0) return 0;
   if (D != V || G <= 0 || H % G) return -1;
+  const AttnExtra ex{softcap, out_scale, sink, gate_wide};
   const dim3 grid((unsigned)n_qtiles, (unsigned)H);
 #define MMA_CASE(DD) case DD: { \
     constexpr int smem = 2 * 64 * (2 * DD + 16) * 2; \
@@ -1138,7 +1187,7 @@ int lbk_masked_attention_mma(const void* q, long ldq, const void* kbase, const v
     if (!once) { cudaFuncSetAttribute(masked_attention_mma_kernel<DD, DD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); once = true; } \
     masked_attention_mma_kernel<DD, DD><<<grid, 128, smem, s>>>((const bf16*)q, ldq, (const bf16*)kbase, \
     (const bf16*)vbase, ldkv, ext_off, nsink, cstart, (const bf16*)gate, ldg, qt_seq, qt_start, seq_off, past, (bf16*)y, ldy, H, G, \
-    window, chunk, keep, scale); } break
+    window, chunk, keep, scale, ex); } break
   switch (D) {
     MMA_CASE(32); MMA_CASE(48); MMA_CASE(64); MMA_CASE(96); MMA_CASE(128);
     default: return -1;
@@ -1149,8 +1198,10 @@ int lbk_masked_attention_mma(const void* q, long ldq, const void* kbase, const v
 
 int lbk_ring_decode(const void* q, long ldq, const void* ring, const void* first, int L, int nfirst, const int* slots, const int* past,
                     const void* gate, long ldg, void* y, long ldy, float* part, int B, int H, int G, int D, int V, int window,
-                    int chunk, int keep, float scale, int splits, int dtype, cudaStream_t s) {
+                    int chunk, int keep, float scale, int splits, float softcap, int sink, int gate_wide, float out_scale, int dtype,
+                    cudaStream_t s) {
   if (B == 0) return 0;
+  const AttnExtra ex{softcap, out_scale, sink, gate_wide};
   if (G <= 0 || H % G || H / G > DEC_MAXR || V > 32 * DEC_MAXVL || splits < 1) return -1;
   const int R = H / G;
   const size_t smem = ((size_t)R * D + 4 * (size_t)R * (V + 2)) * sizeof(float);
@@ -1160,13 +1211,13 @@ int lbk_ring_decode(const void* q, long ldq, const void* ring, const void* first
   if (dtype) {
     const int vec = (D % 8 == 0 && C % 8 == 0 && ((uintptr_t)ring & 15) == 0 && ((uintptr_t)first & 15) == 0) ? 1 : 0;
     ring_decode_kernel<bf16><<<grid, 128, smem, s>>>((const bf16*)q, ldq, (const bf16*)ring, (const bf16*)first, L, nfirst, slots, past,
-                                                     part, H, G, D, V, window, chunk, keep, scale, splits, vec);
-    ring_decode_merge_kernel<bf16><<<dim3((unsigned)B, (unsigned)H), 64, 0, s>>>(part, (const bf16*)gate, ldg, (bf16*)y, ldy, H, V, splits);
+                                                     part, H, G, D, V, window, chunk, keep, scale, splits, vec, softcap);
+    ring_decode_merge_kernel<bf16><<<dim3((unsigned)B, (unsigned)H), 64, 0, s>>>(part, (const bf16*)gate, ldg, (bf16*)y, ldy, H, V, splits, ex);
   } else {
     const int vec = (D % 8 == 0 && C % 4 == 0 && ((uintptr_t)ring & 15) == 0 && ((uintptr_t)first & 15) == 0) ? 1 : 0;
     ring_decode_kernel<float><<<grid, 128, smem, s>>>((const float*)q, ldq, (const float*)ring, (const float*)first, L, nfirst, slots,
-                                                      past, part, H, G, D, V, window, chunk, keep, scale, splits, vec);
-    ring_decode_merge_kernel<float><<<dim3((unsigned)B, (unsigned)H), 64, 0, s>>>(part, (const float*)gate, ldg, (float*)y, ldy, H, V, splits);
+                                                      past, part, H, G, D, V, window, chunk, keep, scale, splits, vec, softcap);
+    ring_decode_merge_kernel<float><<<dim3((unsigned)B, (unsigned)H), 64, 0, s>>>(part, (const float*)gate, ldg, (float*)y, ldy, H, V, splits, ex);
   }
   LAUNCH_END();
 }

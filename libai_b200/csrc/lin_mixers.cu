@@ -1,0 +1,443 @@
+// Kernels of decoders whose sequence mixers are linear-attention recurrences with a decay, on several residual streams:
+// token + bigram embedding, hyper-connection streams fused with the RMS norm that opens the next sublayer, the decayed
+// outer-product recurrence (one fixed decay per head, or one data-dependent decay per key channel) with its fp32 state,
+// and the gated RMS norm of the read-out.
+//
+// Conventions (the same ragged-batch descriptor as seq_mixers.cu / kv_mixers.cu).  A step carries B sequences; sequence
+// b brings n_b = seq_off[b+1]-seq_off[b] new tokens packed at rows seq_off[b].. of every activation matrix, has past[b]
+// tokens already folded into its state, which lives in slot slots[b]; a sequence with past[b] == 0 never reads its slot.
+// Activations are `T` (float or bf16, `dtype` 0 / 1); the residual streams, norms, decays and the recurrence are fp32
+// in both.  Built WITHOUT fast-math: the fp32 mode is exact to rounding.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+namespace {
+
+using bf16 = __nv_bfloat16;
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void stf(T* p, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+// four consecutive channels (16-byte fp32 / 8-byte bf16 accesses)
+template <typename T> __device__ __forceinline__ float4 ld4(const T* p);
+template <> __device__ __forceinline__ float4 ld4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <> __device__ __forceinline__ float4 ld4<bf16>(const bf16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+  return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+template <typename T> __device__ __forceinline__ void st4(T* p, float4 v);
+template <> __device__ __forceinline__ void st4<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <> __device__ __forceinline__ void st4<bf16>(bf16* p, float4 v) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<const uint32_t*>(&a); raw.y = *reinterpret_cast<const uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
+  return v;
+}
+// sum over the block (blockDim.x a multiple of 32, at most 1024); every thread gets the result
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[w] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int i = 0; i < nw; ++i) t += red[i];
+  return t;
+}
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-x)); }
+__device__ __forceinline__ float siluf_(float x) { return x / (1.f + expf(-x)); }
+// log(sigmoid(x)) without cancellation: min(x, 0) - log1p(exp(-|x|))
+__device__ __forceinline__ float logsigmoidf_(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
+
+// ------------------------------------------------------------------------------------------------------------------
+// Embedding: x[r] = table[ids[r]] * scale + bigram[row(r)], written to every one of `ns` residual streams
+// (x: [ns, rows, n] fp32).  row(r) = (previous token * mul_prev + token * mul_cur) mod buckets; the first token of a
+// sequence takes row `buckets`.  The previous token of a step's first row is last[slot] (the sequence's state) when
+// past > 0.  token_last_kernel then stores every sequence's last token of the step (a second launch: the first rows of
+// the step must have read `last` before it changes).
+// ------------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_bigram_kernel(const T* __restrict__ table, const T* __restrict__ bigram, const int64_t* __restrict__ ids,
+                                    const int* __restrict__ last, const int* __restrict__ tok_seq, const int* __restrict__ seq_off,
+                                    const int* __restrict__ slots, const int* __restrict__ past, float scale, long mul_prev,
+                                    long mul_cur, long buckets, float* __restrict__ x, long rows, int n, int ns, int vec) {
+  const long r = blockIdx.x;
+  const int b = tok_seq[r];
+  const long tok = ids[r];
+  long prev = -1;
+  if (r > seq_off[b]) prev = ids[r - 1];
+  else if (past[b] > 0) prev = last[slots[b]];
+  const long row = prev < 0 ? buckets : (prev * mul_prev + tok * mul_cur) % buckets;
+  const T* e = table + tok * n;
+  const T* g = bigram + row * n;
+  if (vec) {
+    for (int c = threadIdx.x * 4; c < n; c += blockDim.x * 4) {
+      const float4 a = ld4(e + c), d = ld4(g + c);
+      const float4 v = make_float4(a.x * scale + d.x, a.y * scale + d.y, a.z * scale + d.z, a.w * scale + d.w);
+      for (int s = 0; s < ns; ++s) *reinterpret_cast<float4*>(x + ((long)s * rows + r) * n + c) = v;
+    }
+  } else {
+    for (int c = threadIdx.x; c < n; c += blockDim.x) {
+      const float v = ldf(e + c) * scale + ldf(g + c);
+      for (int s = 0; s < ns; ++s) x[((long)s * rows + r) * n + c] = v;
+    }
+  }
+}
+
+__global__ void token_last_kernel(const int64_t* __restrict__ ids, int* __restrict__ last, const int* __restrict__ seq_off,
+                                  const int* __restrict__ slots, int B) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b < B) last[slots[b]] = (int)ids[seq_off[b + 1] - 1];
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Hyper-connections: `ns` residual streams x_1..x_ns ([ns, rows, n] fp32, updated in place).  One block per row:
+//   closing a sublayer (y given):   x_t <- sum_s mix[s, t] x_s + out[t] * y     (all t from the old streams; y: rows of
+//                                   the sublayer's output, or - `pos` given - sum_k cw[r,k] * y[pos[r,k]] over sorted
+//                                   expert rows)
+//   opening the next (h given):     u = sum_s inw[s] x_s;  h = u / sqrt(mean(u^2) + eps) * w
+// mix / out / inw are fp32.  u is kept in shared memory between the two passes over the row.
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int HC_MAXS = 8;
+
+template <typename T, typename Ty>
+__global__ void hc_step_kernel(float* __restrict__ x, long rows, int n, int ns, const Ty* __restrict__ y, long ldy,
+                               const int* __restrict__ pos, const float* __restrict__ cw, int top, const float* __restrict__ mix,
+                               const float* __restrict__ outw, const float* __restrict__ inw, const T* __restrict__ w, float eps,
+                               T* __restrict__ h, long ldh, int vec) {
+  extern __shared__ __align__(16) float hc_sm[];
+  float* u = hc_sm;                                  // [n] (only with h)
+  __shared__ float coef[HC_MAXS * HC_MAXS + 2 * HC_MAXS];
+  __shared__ float red[32];
+  const long r = blockIdx.x;
+  if (threadIdx.x < ns * ns) coef[threadIdx.x] = y ? mix[threadIdx.x] : 0.f;
+  if (threadIdx.x < ns) {
+    coef[HC_MAXS * HC_MAXS + threadIdx.x] = y ? outw[threadIdx.x] : 0.f;
+    coef[HC_MAXS * HC_MAXS + HC_MAXS + threadIdx.x] = h ? inw[threadIdx.x] : 0.f;
+  }
+  __syncthreads();
+  const float* cm = coef;
+  const float* co = coef + HC_MAXS * HC_MAXS;
+  const float* ci = co + HC_MAXS;
+  float ss = 0.f;
+  if (vec) {
+    for (int c = threadIdx.x * 4; c < n; c += blockDim.x * 4) {
+      float4 xs[HC_MAXS];
+#pragma unroll
+      for (int s = 0; s < HC_MAXS; ++s) if (s < ns) xs[s] = *reinterpret_cast<const float4*>(x + ((long)s * rows + r) * n + c);
+      if (y) {
+        float4 yv;
+        if (pos) {
+          yv = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int k = 0; k < top; ++k) {
+            const float wk = cw[r * top + k];
+            const float4 t = ld4(y + (long)pos[r * top + k] * ldy + c);
+            yv.x += wk * t.x; yv.y += wk * t.y; yv.z += wk * t.z; yv.w += wk * t.w;
+          }
+        } else {
+          yv = ld4(y + r * ldy + c);
+        }
+        float4 nx[HC_MAXS];
+#pragma unroll
+        for (int t = 0; t < HC_MAXS; ++t) {
+          if (t < ns) {
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int s = 0; s < HC_MAXS; ++s) {
+              if (s < ns) { const float m = cm[s * ns + t]; a.x += m * xs[s].x; a.y += m * xs[s].y; a.z += m * xs[s].z; a.w += m * xs[s].w; }
+            }
+            const float o = co[t];
+            a.x += o * yv.x; a.y += o * yv.y; a.z += o * yv.z; a.w += o * yv.w;
+            nx[t] = a;
+          }
+        }
+#pragma unroll
+        for (int t = 0; t < HC_MAXS; ++t) {
+          if (t < ns) { xs[t] = nx[t]; *reinterpret_cast<float4*>(x + ((long)t * rows + r) * n + c) = nx[t]; }
+        }
+      }
+      if (h) {
+        float4 uv = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int s = 0; s < HC_MAXS; ++s) {
+          if (s < ns) { const float m = ci[s]; uv.x += m * xs[s].x; uv.y += m * xs[s].y; uv.z += m * xs[s].z; uv.w += m * xs[s].w; }
+        }
+        *reinterpret_cast<float4*>(u + c) = uv;
+        ss += uv.x * uv.x + uv.y * uv.y + uv.z * uv.z + uv.w * uv.w;
+      }
+    }
+  } else {
+    for (int c = threadIdx.x; c < n; c += blockDim.x) {
+      float xs[HC_MAXS];
+#pragma unroll
+      for (int s = 0; s < HC_MAXS; ++s) if (s < ns) xs[s] = x[((long)s * rows + r) * n + c];
+      if (y) {
+        float yv = 0.f;
+        if (pos) { for (int k = 0; k < top; ++k) yv += cw[r * top + k] * ldf(y + (long)pos[r * top + k] * ldy + c); }
+        else yv = ldf(y + r * ldy + c);
+        float nx[HC_MAXS];
+#pragma unroll
+        for (int t = 0; t < HC_MAXS; ++t) {
+          if (t < ns) {
+            float a = 0.f;
+#pragma unroll
+            for (int s = 0; s < HC_MAXS; ++s) if (s < ns) a += cm[s * ns + t] * xs[s];
+            nx[t] = a + co[t] * yv;
+          }
+        }
+#pragma unroll
+        for (int t = 0; t < HC_MAXS; ++t) if (t < ns) { xs[t] = nx[t]; x[((long)t * rows + r) * n + c] = nx[t]; }
+      }
+      if (h) {
+        float uv = 0.f;
+#pragma unroll
+        for (int s = 0; s < HC_MAXS; ++s) if (s < ns) uv += ci[s] * xs[s];
+        u[c] = uv;
+        ss += uv * uv;
+      }
+    }
+  }
+  if (!h) return;
+  ss = block_sum(ss, red);
+  const float rr = 1.f / sqrtf(ss / (float)n + eps);
+  if (vec) {
+    for (int c = threadIdx.x * 4; c < n; c += blockDim.x * 4) {
+      const float4 uv = *reinterpret_cast<const float4*>(u + c), wv = ld4(w + c);
+      st4(h + r * ldh + c, make_float4(uv.x * rr * wv.x, uv.y * rr * wv.y, uv.z * rr * wv.z, uv.w * rr * wv.w));
+    }
+  } else {
+    for (int c = threadIdx.x; c < n; c += blockDim.x) stf(h + r * ldh + c, u[c] * rr * ldf(w + c));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Decayed outer-product recurrence (linear attention).  Per head, with S [D, V] in fp32:
+//   S <- diag(a_t) S + k_t v_t^T;   o_t = S^T q_t
+// a_t is one fixed number per head (`decay` [H], `z` absent) or one per key channel and token,
+// a = sigmoid(z + zb)^(inv_tau) = exp(inv_tau * log sigmoid(z + zb)) with the logits z [tokens, H*D] in fp32.
+// q, k, v are column slices of the projection output (row stride ld*); `act` 1 passes them through SiLU; q is
+// multiplied by q_scale and k by k_scale (fp32).  Columns of S are independent: a block owns `VT` of them for one
+// (sequence, head); every column is shared by R adjacent lanes that each keep DPT consecutive rows of it in registers,
+// so a token costs 3*DPT fused multiply-adds per lane and log2(R) shuffle rounds.  Tokens are staged through shared
+// memory `SCAN_CT` at a time as fp32 (rows of lane r at offset r*(DPT+4): 16-byte loads without bank conflicts), with
+// decays, activations and scales applied during staging, so the serial part only touches registers and shared memory.
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int SCAN_CT = 16;
+
+template <typename T, int DPT>
+__global__ void __launch_bounds__(256, DPT <= 16 ? 2 : 1)
+decay_scan_kernel(const T* __restrict__ q, long ldq, const T* __restrict__ k, long ldk, const T* __restrict__ v, long ldv,
+                  const float* __restrict__ decay, const float* __restrict__ z, long ldz, const float* __restrict__ zb, float inv_tau,
+                  float q_scale, float k_scale, int act, float* __restrict__ S, const int* __restrict__ seq_off,
+                  const int* __restrict__ slots, const int* __restrict__ past, float* __restrict__ out, int H, int D, int V, int R,
+                  int VT) {
+  extern __shared__ __align__(16) float sm[];
+  constexpr int PS = DPT + 4;                   // padded stride of one lane's rows
+  const int b = blockIdx.x / H, h = blockIdx.x % H;
+  const int j0 = blockIdx.y * VT;
+  const int Dr = R * DPT;                       // rows covered (rows >= D hold zeros)
+  const int Dp = R * PS;                        // floats per staged token
+  const bool chan = z != nullptr;
+  float* sk = sm;                               // [CT][Dp]
+  float* sq = sk + SCAN_CT * Dp;                // [CT][Dp]
+  float* sg = sq + SCAN_CT * Dp;                // [CT][Dp] (chan) or nothing
+  float* sv = sg + (chan ? SCAN_CT * Dp : 0);   // [CT][VT]
+  const int tid = threadIdx.x, nth = blockDim.x;
+  const int r = tid % R, jj = tid / R, j = j0 + jj;
+  const bool col_ok = jj < VT && j < V;
+  const int n = seq_off[b + 1] - seq_off[b];
+  const long tok0 = seq_off[b];
+  const float g0 = chan ? 1.f : decay[h];
+  float* Sg = S + ((long)slots[b] * H + h) * (long)D * V;
+  float s[DPT];
+#pragma unroll
+  for (int d = 0; d < DPT; ++d) {
+    const int i = r * DPT + d;
+    s[d] = (past[b] > 0 && col_ok && i < D) ? Sg[(long)i * V + j] : 0.f;
+  }
+  for (int c0 = 0; c0 < n; c0 += SCAN_CT) {
+    const int ct = min(SCAN_CT, n - c0);
+    __syncthreads();
+    for (int e = tid; e < ct * Dr; e += nth) {
+      const int t = e / Dr, i = e - t * Dr;
+      const int at = t * Dp + (i / DPT) * PS + (i % DPT);
+      const long row = tok0 + c0 + t;
+      const bool in = i < D;
+      float kv = in ? ldf(k + row * ldk + h * D + i) : 0.f, qv = in ? ldf(q + row * ldq + h * D + i) : 0.f;
+      if (act) { kv = siluf_(kv); qv = siluf_(qv); }
+      sk[at] = kv * k_scale;
+      sq[at] = qv * q_scale;
+      if (chan) sg[at] = in ? expf(inv_tau * logsigmoidf_(z[row * ldz + h * D + i] + zb[h * D + i])) : 1.f;
+    }
+    for (int e = tid; e < ct * VT; e += nth) {
+      const int t = e / VT, c = e - t * VT;
+      float vv = (j0 + c < V) ? ldf(v + (tok0 + c0 + t) * ldv + h * V + j0 + c) : 0.f;
+      if (act) vv = siluf_(vv);
+      sv[e] = vv;
+    }
+    __syncthreads();
+    // every thread walks the tokens (lanes of idle columns included: the shuffles below name the whole warp)
+    for (int t = 0; t < ct; ++t) {
+      float pq[4] = {0.f, 0.f, 0.f, 0.f};
+      const float4* k4 = reinterpret_cast<const float4*>(sk + t * Dp + r * PS);
+      const float4* q4 = reinterpret_cast<const float4*>(sq + t * Dp + r * PS);
+      const float4* g4 = reinterpret_cast<const float4*>(sg + t * Dp + r * PS);
+      const float vt = jj < VT ? sv[t * VT + jj] : 0.f;
+#pragma unroll
+      for (int d4 = 0; d4 < DPT / 4; ++d4) {
+        const float4 kx = k4[d4], qx = q4[d4];
+        float4 gx = make_float4(g0, g0, g0, g0);
+        if (chan) gx = g4[d4];
+        s[4 * d4] = s[4 * d4] * gx.x + kx.x * vt; s[4 * d4 + 1] = s[4 * d4 + 1] * gx.y + kx.y * vt;
+        s[4 * d4 + 2] = s[4 * d4 + 2] * gx.z + kx.z * vt; s[4 * d4 + 3] = s[4 * d4 + 3] * gx.w + kx.w * vt;
+        pq[0] += s[4 * d4] * qx.x; pq[1] += s[4 * d4 + 1] * qx.y; pq[2] += s[4 * d4 + 2] * qx.z; pq[3] += s[4 * d4 + 3] * qx.w;
+      }
+      float o = (pq[0] + pq[1]) + (pq[2] + pq[3]);
+      for (int m = R >> 1; m > 0; m >>= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
+      if (r == 0 && col_ok) out[(tok0 + c0 + t) * (long)(H * V) + h * V + j] = o;
+    }
+  }
+  if (col_ok) {
+#pragma unroll
+    for (int d = 0; d < DPT; ++d) { const int i = r * DPT + d; if (i < D) Sg[(long)i * V + j] = s[d]; }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Gated RMS norm of a read-out o [rows, H*V] (fp32):  y = o / sqrt(mean(o^2) + eps) * w * act(gate) * out_scale, the
+// mean taken over the V channels of every head (per_head = 1, w [V] shared by the heads or absent) or over the whole
+// row (per_head = 0, w [H*V] or absent); act 0: silu, 1: sigmoid.  One warp per (row, head), or one block per row.
+// ------------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void gated_norm_head_kernel(const float* __restrict__ o, const T* __restrict__ gate, long ldg, const T* __restrict__ w,
+                                       float eps, int act, float out_scale, T* __restrict__ y, long ldy, long rows, int H, int V) {
+  const long wid = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (wid >= rows * H) return;
+  const long tok = wid / H; const int h = (int)(wid - tok * H);
+  const float* orow = o + (tok * H + h) * (long)V;
+  float ss = 0.f;
+  for (int i = lane; i < V; i += 32) ss += orow[i] * orow[i];
+  ss = warp_sum(ss);
+  const float rr = out_scale / sqrtf(ss / (float)V + eps);
+  for (int i = lane; i < V; i += 32) {
+    const float g = ldf(gate + tok * ldg + h * V + i);
+    const float ga = act == 0 ? siluf_(g) : sigmoidf_(g);
+    stf(y + tok * ldy + h * V + i, orow[i] * rr * (w ? ldf(w + i) : 1.f) * ga);
+  }
+}
+
+template <typename T>
+__global__ void gated_norm_row_kernel(const float* __restrict__ o, const T* __restrict__ gate, long ldg, const T* __restrict__ w,
+                                      float eps, int act, float out_scale, T* __restrict__ y, long ldy, int n) {
+  __shared__ float red[32];
+  const long tok = blockIdx.x;
+  const float* orow = o + tok * (long)n;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) ss += orow[i] * orow[i];
+  ss = block_sum(ss, red);
+  const float rr = out_scale / sqrtf(ss / (float)n + eps);
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float g = ldf(gate + tok * ldg + i);
+    const float ga = act == 0 ? siluf_(g) : sigmoidf_(g);
+    stf(y + tok * ldy + i, orow[i] * rr * (w ? ldf(w + i) : 1.f) * ga);
+  }
+}
+
+}  // namespace
+
+// ====================================================================================================================
+// launchers (C ABI; return 0, a CUDA error code, or -1 for sizes a kernel is not built for)
+// ====================================================================================================================
+#define LAUNCH_END() do { const cudaError_t e_ = cudaGetLastError(); return e_ == cudaSuccess ? 0 : (int)e_; } while (0)
+
+extern "C" {
+
+int lbl_embed_bigram(const void* table, const void* bigram, const int64_t* ids, int* last, const int* tok_seq, const int* seq_off,
+                     const int* slots, const int* past, float scale, long mul_prev, long mul_cur, long buckets, float* x, long rows,
+                     int n, int ns, int B, int dtype, cudaStream_t s) {
+  if (rows == 0) return 0;
+  const int vec = (n % 4 == 0 && ((uintptr_t)table & 15) == 0 && ((uintptr_t)bigram & 15) == 0 && ((uintptr_t)x & 15) == 0) ? 1 : 0;
+  const int threads = n >= 1024 ? 256 : 128;
+  if (dtype) embed_bigram_kernel<bf16><<<(unsigned)rows, threads, 0, s>>>((const bf16*)table, (const bf16*)bigram, ids, last, tok_seq,
+      seq_off, slots, past, scale, mul_prev, mul_cur, buckets, x, rows, n, ns, vec);
+  else embed_bigram_kernel<float><<<(unsigned)rows, threads, 0, s>>>((const float*)table, (const float*)bigram, ids, last, tok_seq,
+      seq_off, slots, past, scale, mul_prev, mul_cur, buckets, x, rows, n, ns, vec);
+  token_last_kernel<<<(B + 127) / 128, 128, 0, s>>>(ids, last, seq_off, slots, B);
+  LAUNCH_END();
+}
+
+int lbl_hc_step(float* x, long rows, int n, int ns, const void* y, long ldy, int ydtype, const int* pos, const float* cw, int top,
+                const float* mix, const float* outw, const float* inw, const void* w, float eps, void* h, long ldh, int dtype,
+                cudaStream_t s) {
+  if (rows == 0) return 0;
+  if (ns < 1 || ns > HC_MAXS) return -1;
+  const size_t smem = h ? (size_t)n * sizeof(float) : 0;
+  if (smem > 160 * 1024) return -1;
+  int vec = (n % 4 == 0 && ((uintptr_t)x & 15) == 0) ? 1 : 0;
+  if (y && (((uintptr_t)y & 15) != 0 || ldy % 4 != 0)) vec = 0;
+  if (h && (((uintptr_t)h & 15) != 0 || ldh % 4 != 0 || ((uintptr_t)w & 15) != 0)) vec = 0;
+  const int threads = n >= 2048 ? 256 : 128;
+#define HC(TT, TY) { \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(hc_step_kernel<TT, TY>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    hc_step_kernel<TT, TY><<<(unsigned)rows, threads, smem, s>>>(x, rows, n, ns, (const TY*)y, ldy, pos, cw, top, mix, outw, inw, \
+                                                                 (const TT*)w, eps, (TT*)h, ldh, vec); }
+  if (dtype) { if (ydtype) HC(bf16, bf16) else HC(bf16, float) }
+  else { if (ydtype) return -1; HC(float, float) }
+#undef HC
+  LAUNCH_END();
+}
+
+int lbl_decay_scan(const void* q, long ldq, const void* k, long ldk, const void* v, long ldv, const float* decay, const float* z,
+                   long ldz, const float* zb, float inv_tau, float q_scale, float k_scale, int act, float* S, const int* seq_off,
+                   const int* slots, const int* past, float* out, int B, int H, int D, int V, int dtype, cudaStream_t s) {
+  if (B == 0) return 0;
+  if (D > 256 || (!decay && !z) || (z && !zb)) return -1;
+  const int dpt = D <= 32 ? 8 : (D <= 128 ? 16 : 32);  // rows per lane: 4 lanes per column up to D = 64, 8 lanes up to 256
+  int R = 1;
+  while (R * dpt < D) R <<= 1;                   // a power of two <= 8
+  int VT = R <= 4 ? 64 : 32;                     // columns per block (columns are independent: more blocks per head)
+  if (V < VT) VT = V;
+  const int threads = ((VT * R + 31) / 32) * 32;
+  const int Dp = R * (dpt + 4);
+  const size_t smem = sizeof(float) * ((size_t)SCAN_CT * Dp * (z ? 3 : 2) + (size_t)SCAN_CT * VT);
+  const dim3 grid((unsigned)(B * H), (unsigned)((V + VT - 1) / VT));
+#define DS(TT, P) { \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(decay_scan_kernel<TT, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    decay_scan_kernel<TT, P><<<grid, threads, smem, s>>>((const TT*)q, ldq, (const TT*)k, ldk, (const TT*)v, ldv, decay, z, ldz, zb, \
+        inv_tau, q_scale, k_scale, act, S, seq_off, slots, past, out, H, D, V, R, VT); }
+  if (dtype == 0) { if (dpt == 8) DS(float, 8) else if (dpt == 16) DS(float, 16) else DS(float, 32) }
+  else { if (dpt == 8) DS(bf16, 8) else if (dpt == 16) DS(bf16, 16) else DS(bf16, 32) }
+#undef DS
+  LAUNCH_END();
+}
+
+int lbl_gated_norm(const float* o, const void* gate, long ldg, const void* w, float eps, int act, float out_scale, void* y, long ldy,
+                   long rows, int H, int V, int per_head, int dtype, cudaStream_t s) {
+  if (rows == 0) return 0;
+  if (per_head) {
+    const unsigned grid = (unsigned)((rows * H * 32 + 255) / 256);
+    if (dtype) gated_norm_head_kernel<bf16><<<grid, 256, 0, s>>>(o, (const bf16*)gate, ldg, (const bf16*)w, eps, act, out_scale, (bf16*)y, ldy, rows, H, V);
+    else gated_norm_head_kernel<float><<<grid, 256, 0, s>>>(o, (const float*)gate, ldg, (const float*)w, eps, act, out_scale, (float*)y, ldy, rows, H, V);
+  } else {
+    const int n = H * V, threads = n >= 1024 ? 256 : 128;
+    if (dtype) gated_norm_row_kernel<bf16><<<(unsigned)rows, threads, 0, s>>>(o, (const bf16*)gate, ldg, (const bf16*)w, eps, act, out_scale, (bf16*)y, ldy, n);
+    else gated_norm_row_kernel<float><<<(unsigned)rows, threads, 0, s>>>(o, (const float*)gate, ldg, (const float*)w, eps, act, out_scale, (float*)y, ldy, n);
+  }
+  LAUNCH_END();
+}
+
+}  // extern "C"

@@ -7,8 +7,9 @@ A model registers one entry per layer run (a layer that is run several times in 
 * ``"kv"`` — a ring of the last ``ring_len`` key/value rows of an attention layer whose mask reaches back a bounded number
   of positions, ``[slots, ring_len, C]`` (position ``p`` at ``p % ring_len``), and the rows of the first ``first_len``
   positions, ``[slots, first_len, C]``, which a mask that keeps the first tokens goes on reading after they left the ring;
-* ``"recurrent"`` — the matrix state of a delta-rule layer, ``[slots, H, D, V]`` in fp32, and the last ``taps - 1`` inputs
-  of its short convolutions, ``[slots, taps - 1, C]``.
+* ``"recurrent"`` — the matrix state of a delta-rule or linear-attention layer, ``[slots, H, D, V]`` in fp32, and the last
+  ``taps - 1`` inputs of its short convolutions, ``[slots, taps - 1, C]`` (empty for a layer without convolutions);
+* ``"token"`` — the last token of the sequence, ``[slots]`` int32 (an embedding that looks at the previous token).
 
 A request holds one slot in every entry from its first token until it is finished.  Slots are handed out from a free list
 and reused as they come back; a reused slot is not cleared — the kernels ignore a slot's contents for a sequence whose
@@ -34,8 +35,8 @@ class SequenceStateCache:
     # ------------------------------------------------------------------ layout
     def register(self, kind: str, **shape) -> int:
         """Add one entry; returns its handle.  ``latent``: ``ring_len, channels``; ``kv``: ``ring_len, first_len, channels``;
-        ``recurrent``: ``heads, dim, vdim, taps, conv_channels``."""
-        assert kind in ("latent", "kv", "recurrent"), kind
+        ``recurrent``: ``heads, dim, vdim, taps, conv_channels``; ``token``: nothing."""
+        assert kind in ("latent", "kv", "recurrent", "token"), kind
         self._specs.append(dict(kind=kind, **shape))
         self._bufs.append(self._make(self._specs[-1], self.capacity))
         return len(self._specs) - 1
@@ -46,6 +47,8 @@ class SequenceStateCache:
         if spec["kind"] == "kv":
             return {"ring": torch.zeros(n, spec["ring_len"], spec["channels"], dtype=self.dtype, device=self.device),
                     "first": torch.zeros(n, spec["first_len"], spec["channels"], dtype=self.dtype, device=self.device)}
+        if spec["kind"] == "token":
+            return {"last": torch.zeros(n, dtype=torch.int32, device=self.device)}
         return {
             "S": torch.zeros(n, spec["heads"], spec["dim"], spec["vdim"], dtype=torch.float32, device=self.device),
             "tail": torch.zeros(n, max(spec["taps"] - 1, 0), spec["conv_channels"], dtype=self.dtype, device=self.device),

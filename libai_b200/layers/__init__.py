@@ -16,7 +16,9 @@ __all__ = [
     "MultiheadAttention", "AttnMaskType", "ParallelCrossEntropyLoss", "LMLogits", "DropPath",
 ]
 from .delta_rule import GatedDeltaMixer
+from .hyper_connections import HyperConnection
 from .latent_attention import LatentAttention
 from .layer_norm import DynamicTanh
+from .linear_attention import DecayLinearAttention
 from .moe import MoEFeedForward
 from .ring_attention import RingAttention

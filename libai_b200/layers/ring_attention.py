@@ -9,8 +9,12 @@ Options, all constructor arguments:
   :func:`libai_b200.ops.kv_functional.rotary_frequencies` (optionally blended per dimension towards ``f / factor``);
 * the mask: ``chunk`` — position i sees j ≤ i of its own chunk of that many positions (chunks are counted from position 0
   of the sequence); or ``window`` with ``keep_first`` — j ≤ i with ``i − j < window`` or ``j < keep_first``;
-* ``out_gate`` — head h of the result is multiplied by ``sigmoid(W_g h)_h``;
-* ``kv_source`` — the layer has no key/value projections and reads the cache of another layer (keys as that layer stored them).
+* ``out_gate`` — head h of the result is multiplied by ``sigmoid(W_g h)_h`` (``True`` / ``"head"``: one gate logit per head),
+  or every channel of the concatenated heads by its own ``sigmoid(W_g h)`` (``"channel"``: ``W_g`` is ``[H·V, width]``);
+* ``kv_source`` — the layer has no key/value projections and reads the cache of another layer (keys as that layer stored them);
+* ``value_from_key`` — there is no ``W_v``: the values are the keys as projected, before norm and rotation (``vdim = dim``);
+* ``softcap`` — scaled scores pass through ``cap · tanh(score / cap)``; ``sink`` — the softmax has one more entry of score 0
+  that carries no value: ``p_j = exp(s_j) / (1 + Σ exp(s))``.
 
 State per sequence (:class:`libai_b200.inference.state_cache.SequenceStateCache`, kind ``kv``): a ring of the last
 ``ring_len`` rows ``[keys | values]`` and the rows of the first ``first_len`` positions.  Prompt steps read
@@ -33,10 +37,14 @@ from ._param import create_parameter, ones_, xavier_normal_
 class RingAttention(nn.Module):
     def __init__(self, width, heads, kv_heads, dim, vdim, *, window=0, chunk=0, keep_first=0, scale=None, rot_dims=0,
                  rot_base=10000.0, rot_scaling=None, qk_norm: Optional[str] = None, out_gate=False, kv_source: Optional[int] = None,
-                 eps=1e-6, init_method=xavier_normal_, layer_idx=0):
+                 value_from_key=False, softcap=None, sink=False, eps=1e-6, init_method=xavier_normal_, layer_idx=0):
         super().__init__()
         assert heads % kv_heads == 0 and (chunk > 0) != (window > 0), "one of chunk / window bounds the mask"
         assert qk_norm in (None, "full", "head_unit") and rot_dims % 2 == 0 and rot_dims <= dim
+        assert out_gate in (False, True, None, "head", "channel")
+        assert not value_from_key or (vdim == dim and kv_source is None), "values that are the keys have the keys' size"
+        self.value_from_key, self.softcap, self.sink = bool(value_from_key), float(softcap or 0.0), bool(sink)
+        self.gate_wide = out_gate == "channel"
         self.width, self.heads, self.kv_heads, self.dim, self.vdim = width, heads, kv_heads, dim, vdim
         self.window, self.chunk, self.keep_first = int(window), int(chunk), int(keep_first) if window > 0 else 0
         self.scale, self.eps, self.qk_norm, self.kv_source = float(scale if scale is not None else dim ** -0.5), eps, qk_norm, kv_source
@@ -45,11 +53,12 @@ class RingAttention(nn.Module):
         self.q = mk((heads * dim, width))
         self.q_norm = mk((heads * dim,), ones_) if qk_norm == "full" else None
         if kv_source is None:
-            self.k, self.v = mk((kv_heads * dim, width)), mk((kv_heads * vdim, width))
+            self.k = mk((kv_heads * dim, width))
+            self.v = None if value_from_key else mk((kv_heads * vdim, width))
             self.k_norm = mk((kv_heads * dim,), ones_) if qk_norm == "full" else None
         else:
             self.k = self.v = self.k_norm = None
-        self.g = mk((heads, width)) if out_gate else None
+        self.g = mk((heads * vdim if self.gate_wide else heads, width)) if out_gate else None
         self.o = mk((width, heads * vdim))
         freq, self.rot_mscale = KF.rotary_frequencies(self.rot_dims, rot_base, rot_scaling) if rot_dims else (torch.zeros(0), 1.0)
         self.register_buffer("rot_freq", freq.float(), persistent=False)
@@ -75,8 +84,8 @@ class RingAttention(nn.Module):
 
     def input_weights(self):
         out = [("q", self.q)]
-        if self.kv_source is None:
-            out += [("k", self.k), ("v", self.v)]
+        if self.kv_source is None:                            # values that are the keys: W_k twice in the stacked product
+            out += [("k", self.k), ("v", self.k if self.value_from_key else self.v)]
         if self.g is not None:
             out.append(("g", self.g))
         return out
@@ -84,10 +93,11 @@ class RingAttention(nn.Module):
     def output_weight(self):
         return self.o
 
-    def mix(self, parts, rb, bufs, y, shared):
+    def mix(self, parts, rb, bufs, y, shared, out_scale: float = 1.0):
         """``parts``: the projections of the step's rows (column slices of one product); ``bufs``: the cache entry this layer
         reads; ``shared``: per-step dictionary through which a layer hands the key / value rows of a prompt step to the layers
-        that read its cache; ``y`` ``[tokens, H·V]`` receives the heads' outputs."""
+        that read its cache; ``y`` ``[tokens, H·V]`` receives the heads' outputs (gated, times ``out_scale``)."""
+        extra = dict(softcap=self.softcap, sink=self.sink, gate_wide=self.gate_wide, out_scale=out_scale)
         H, G, D, V = self.heads, self.kv_heads, self.dim, self.vdim
         q, k, v, gate = parts["q"], parts.get("k"), parts.get("v"), parts.get("g")
         if self.rot_freq.device != q.device:
@@ -99,7 +109,7 @@ class RingAttention(nn.Module):
         if rb.single:
             if own:
                 KF.kv_write(ring, first, k, v, rb)
-            KF.ring_attention(q, ring, first, gate, rb, y, H, G, D, V, self.window, self.chunk, self.keep_first, self.scale)
+            KF.ring_attention(q, ring, first, gate, rb, y, H, G, D, V, self.window, self.chunk, self.keep_first, self.scale, **extra)
             return y
         if own:
             ext = rb.kv_ext(self.cache_masks)
@@ -112,7 +122,7 @@ class RingAttention(nn.Module):
             KF.kv_write(ring, first, k, v, rb)
         else:
             ext, kmat, vmat = shared[self.kv_source]
-        KF.masked_attention(q, kmat, vmat, ext, gate, rb, y, H, G, D, V, self.window, self.chunk, self.keep_first, self.scale)
+        KF.masked_attention(q, kmat, vmat, ext, gate, rb, y, H, G, D, V, self.window, self.chunk, self.keep_first, self.scale, **extra)
         return y
 
     def forward(self, h, rb, bufs, shared=None):

@@ -5,6 +5,7 @@ from .nefelorn_model import NefelornForCausalLM, NefelornModel
 from .gpt_model import GPTForPreTraining, GPTModel
 from .llama_model import LlamaForCausalLM, LlamaModel
 from .resmlp import ResMLP
+from .salizen_model import SalizenForCausalLM, SalizenModel
 from .roberta_model import RobertaForCausalLM, RobertaForPreTraining, RobertaModel
 from .swin_transformer import SwinTransformer
 from .swin_transformer_v2 import SwinTransformerV2
@@ -20,4 +21,5 @@ __all__ = [
     "VisionTransformer", "SwinTransformer", "SwinTransformerV2", "ResMLP",
     "LlamaModel", "LlamaForCausalLM",
     "BumodraModel", "BumodraForCausalLM", "NefelornModel", "NefelornForCausalLM",
+    "SalizenModel", "SalizenForCausalLM",
 ]

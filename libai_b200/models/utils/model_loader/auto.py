@@ -35,15 +35,23 @@ def _nefelorn():
     return NefelornForCausalLM, NefelornLoader, {}
 
 
+def _salizen():
+    from libai_b200.models import SalizenForCausalLM
+    from .salizen_loader import SalizenLoader
+
+    return SalizenForCausalLM, SalizenLoader, {}
+
+
 ARCHITECTURES = {
     "bumodra": _bumodra,
     "nefelorn": _nefelorn,
+    "salizen": _salizen,
     "llama": _llama, "llamaforcausallm": _llama,
 }
 
 
 # native libraries (``libai_b200.ops.build``) that a model's generation path launches besides the GEMM library ``_C``
-NATIVE_LIBS = {"bumodra": ["_C_seq"], "nefelorn": ["_C_kv"]}
+NATIVE_LIBS = {"bumodra": ["_C_seq"], "nefelorn": ["_C_kv"], "salizen": ["_C_kv", "_C_lin"]}
 
 
 def native_libs_of(path: str, dtype=torch.bfloat16):

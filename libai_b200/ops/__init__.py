@@ -118,6 +118,27 @@ def load_kv_ext():
     return _KV_EXT
 
 
+_LIN_EXT = None
+_LIN_SO_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "_C_lin.so")
+
+
+def load_lin_ext():
+    """Load ``libai_b200/_C_lin.so`` (bigram embedding, hyper-connection streams, decayed linear-attention recurrences) once; it
+    is compiled in-tree on first use when the checkout has no built copy yet.  Returns ``torch.ops.libai_b200_lin``."""
+    global _LIN_EXT
+    if _LIN_EXT is not None:
+        return _LIN_EXT
+    with _LOCK:
+        if _LIN_EXT is None:
+            if not os.path.exists(_LIN_SO_PATH):
+                from . import build as _build
+
+                _build.build(only=["_C_lin"])
+            torch.ops.load_library(_LIN_SO_PATH)
+            _LIN_EXT = _FastOps(torch.ops.libai_b200_lin)
+    return _LIN_EXT
+
+
 def use_native(*tensors) -> bool:
     """True when the native sm_100a kernel must be used for these tensors."""
     if impl() != "native":

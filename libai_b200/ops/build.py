@@ -1,8 +1,9 @@
 """In-tree build of the native extensions: ``libai_b200/_C.so`` (GEMM, attention, norms, optimizer, collectives) and
-``libai_b200/_C_seq.so`` (ragged-batch sequence mixers with per-sequence state) and ``libai_b200/_C_kv.so`` (ring key/value
-caches, masked grouped-query attention, Dynamic-Tanh norms, mixture of experts).
+``libai_b200/_C_seq.so`` (ragged-batch sequence mixers with per-sequence state), ``libai_b200/_C_kv.so`` (ring key/value
+caches, masked grouped-query attention, Dynamic-Tanh norms, mixture of experts) and ``libai_b200/_C_lin.so`` (bigram embedding,
+hyper-connection streams, decayed linear-attention recurrences).
 
-    python -m libai_b200.ops.build [--force] [--verbose] [--only _C|_C_seq|_C_kv]
+    python -m libai_b200.ops.build [--force] [--verbose] [--only _C|_C_seq|_C_kv|_C_lin]
 
 CUDA sources are compiled for sm_100a only (``-gencode arch=compute_100a,code=sm_100a -lineinfo``);
 nvcc cross-compiles without a GPU.  Objects are cached under ``libai_b200/csrc/build`` keyed by
@@ -32,6 +33,9 @@ SEQ_CPP_SOURCES = ["seq_bindings.cpp"]
 KV_SO_PATH = os.path.join(ROOT, "_C_kv.so")
 KV_CU_SOURCES = ["kv_mixers.cu"]
 KV_CPP_SOURCES = ["kv_bindings.cpp"]
+LIN_SO_PATH = os.path.join(ROOT, "_C_lin.so")
+LIN_CU_SOURCES = ["lin_mixers.cu"]
+LIN_CPP_SOURCES = ["lin_bindings.cpp"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "--use_fast_math", "-std=c++17",
@@ -58,13 +62,17 @@ def _stale(src, obj, deps=()):
 
 
 def build(force: bool = False, verbose: bool = False, only=None) -> str:
-    """Build the libraries named in ``only`` (default: all); returns the path of ``_C.so``."""
-    if only is None or "_C_kv" in only:
-        _build_lib(KV_SO_PATH, KV_CU_SOURCES, KV_CPP_SOURCES, SEQ_NVCC_FLAGS, "_C_kv", force, verbose)
-    if only is None or "_C_seq" in only:
-        _build_lib(SEQ_SO_PATH, SEQ_CU_SOURCES, SEQ_CPP_SOURCES, SEQ_NVCC_FLAGS, "_C_seq", force, verbose)
-    if only is None or "_C" in only:
-        _build_lib(SO_PATH, CU_SOURCES, CPP_SOURCES, NVCC_FLAGS, "_C", force, verbose)
+    """Build the libraries named in ``only`` (default: all), side by side; returns the path of ``_C.so``."""
+    libs = [(KV_SO_PATH, KV_CU_SOURCES, KV_CPP_SOURCES, SEQ_NVCC_FLAGS, "_C_kv"),
+            (LIN_SO_PATH, LIN_CU_SOURCES, LIN_CPP_SOURCES, SEQ_NVCC_FLAGS, "_C_lin"),
+            (SEQ_SO_PATH, SEQ_CU_SOURCES, SEQ_CPP_SOURCES, SEQ_NVCC_FLAGS, "_C_seq"),
+            (SO_PATH, CU_SOURCES, CPP_SOURCES, NVCC_FLAGS, "_C")]
+    libs = [lib for lib in libs if only is None or lib[4] in only]
+    import torch  # noqa: F401  (imported before the threads start: the first import is not thread-safe)
+    from torch.utils import cpp_extension  # noqa: F401
+
+    with ThreadPoolExecutor(max_workers=max(1, len(libs))) as ex:
+        list(ex.map(lambda lib: _build_lib(*lib, force, verbose), libs))
     return SO_PATH
 
 
@@ -115,6 +123,6 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
-    ap.add_argument("--only", action="append", choices=["_C", "_C_seq", "_C_kv"])
+    ap.add_argument("--only", action="append", choices=["_C", "_C_seq", "_C_kv", "_C_lin"])
     a = ap.parse_args()
     print(build(a.force, a.verbose, a.only))

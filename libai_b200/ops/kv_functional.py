@@ -128,11 +128,20 @@ def rotary_frequencies(dims: int, base: float, scaling: Optional[dict] = None):
     """Per-pair angular frequencies ``[dims/2]`` (fp32) and the factor on cos / sin.  Plain: ``f_i = base^(-2i/dims)``, factor 1.
     With ``scaling`` = ``{factor, original, fast, slow}`` the frequencies are blended per dimension between ``f_i`` (dimensions
     that turn more than ``fast`` times within ``original`` positions) and ``f_i / factor`` (fewer than ``slow`` turns), linearly
-    in the dimension index in between, and cos / sin are multiplied by ``0.1 ln(factor) + 1``."""
+    in the dimension index in between, and cos / sin are multiplied by ``0.1 ln(factor) + 1``.  With ``scaling`` =
+    ``{factor, original, low, high}`` the blend is by wavelength ``λ = 2π / f``: ``f`` stays where ``λ < original / high``, becomes
+    ``f / factor`` where ``λ > original / low`` and ``(1 − s) f / factor + s f`` with ``s = (original / λ − low) / (high − low)`` in
+    between; cos / sin keep the factor 1."""
     i = torch.arange(dims // 2, dtype=torch.float64)
     f = float(base) ** (-2.0 * i / dims)
     mscale = 1.0
-    if scaling:
+    if scaling and "low" in scaling:
+        factor, original, low, high = (float(scaling[k]) for k in ("factor", "original", "low", "high"))
+        turns = original * f / (2.0 * math.pi)                                 # original / wavelength
+        s = (turns - low) / (high - low) if high != low else torch.ones_like(turns)
+        blended = (1.0 - s) * f / factor + s * f
+        f = torch.where(turns > high, f, torch.where(turns < low, f / factor, blended))
+    elif scaling:
         factor, original = float(scaling["factor"]), float(scaling["original"])
 
         def turns_dim(t):
@@ -228,37 +237,55 @@ def _visible(pi: int, window: int, chunk: int, keep: int):
     return first + list(range(lo, pi + 1))
 
 
-def _attend_rows(qrow, keys, vals, H, G, D, V, scale):
+def _attend_rows(qrow, keys, vals, H, G, D, V, scale, softcap=0.0, sink=False):
     """``qrow`` ``[H·D]``; ``keys`` ``[n, G·D]``, ``vals`` ``[n, G·V]`` → ``[H, V]`` fp32."""
     rep = H // G
     k = keys.float().view(-1, G, D).repeat_interleave(rep, 1)
     v = vals.float().view(-1, G, V).repeat_interleave(rep, 1)
     s = torch.einsum("hd,jhd->hj", qrow.float().view(H, D), k) * scale
-    return torch.einsum("hj,jhv->hv", torch.softmax(s, -1), v)
+    if softcap:
+        s = softcap * torch.tanh(s / softcap)
+    if sink:                                                    # one more entry of score 0 that carries no value
+        p = torch.softmax(torch.cat([s, s.new_zeros(H, 1)], -1), -1)[:, :-1]
+    else:
+        p = torch.softmax(s, -1)
+    return torch.einsum("hj,jhv->hv", p, v)
+
+
+def _gated(o, gate_row, wide: bool, out_scale: float):
+    """``o`` ``[H, V]`` times ``sigmoid`` of the row's gate logits (one per head, or — ``wide`` — one per channel) and ``out_scale``."""
+    if gate_row is not None:
+        g = torch.sigmoid(gate_row.float())
+        o = o * (g.view(o.shape) if wide else g[:, None])
+    return o * out_scale if out_scale != 1.0 else o
 
 
 def masked_attention(q, kmat, vmat, ext, gate, rb, y, H: int, G: int, D: int, V: int, window: int, chunk: int, keep: int,
-                     scale: float, mma: bool = True):
+                     scale: float, mma: bool = True, softcap: float = 0.0, sink: bool = False, gate_wide: bool = False,
+                     out_scale: float = 1.0):
     """Grouped-query softmax attention of every packed query over the rows of the ext matrix (``kmat`` ``[rows, G·D]``,
     ``vmat`` ``[rows, G·V]``: column slices with one row stride) that its mask admits: position j ≤ i with
     ``j ≥ ⌊i/chunk⌋·chunk`` (``chunk > 0``) or ``j > i − window or j < keep`` (``window > 0``).  Head h of the result is
-    multiplied by ``sigmoid(gate[t, h])`` when a gate is given.  bf16 inputs with head sizes the tensor-core kernel is built for
-    take it; ``mma=False`` keeps them on the generic kernel (fp32 inputs always are)."""
+    multiplied by ``sigmoid(gate[t, h])`` when a gate is given (``gate_wide``: channel c of head h by
+    ``sigmoid(gate[t, h·V + c])``) and by ``out_scale``.  ``softcap`` > 0: scaled scores pass through ``cap · tanh(s / cap)``;
+    ``sink``: the softmax has one more entry of score 0 without a value.  bf16 inputs with head sizes the tensor-core kernel is
+    built for take it; ``mma=False`` keeps them on the generic kernel (fp32 inputs always are)."""
     if _native(q):
         count_launch()
         tiles = (None, None)
-        if mma and q.dtype == torch.bfloat16 and mma_eligible(q, kmat, vmat, y, D, V):
+        if mma and q.dtype == torch.bfloat16 and mma_eligible(q, kmat, vmat, y, D, V) and (
+                gate is None or not gate_wide or (gate.data_ptr() % 4 == 0 and gate.stride(0) % 2 == 0 and V % 2 == 0)):
             tiles = rb.query_tiles(64)
         load_kv_ext().masked_attention(q, kmat, vmat, ext.ext_off, ext.nsink, ext.cstart, gate, rb.tok_seq, rb.seq_off, rb.past,
-                                       tiles[0], tiles[1], y, H, G, D, V, window, chunk, keep, float(scale))
+                                       tiles[0], tiles[1], y, H, G, D, V, window, chunk, keep, float(scale), float(softcap), bool(sink),
+                                       bool(gate_wide), float(out_scale))
         return y
     for b in range(rb.B):
         lo, n, past, eo, ns, cs = rb.offsets[b], rb.lens[b], rb.past_list[b], ext.offsets[b], ext.nsink_list[b], ext.cstart_list[b]
         for t in range(n):
             rows = [eo + (p if p < cs else ns + p - cs) for p in _visible(past + t, window, chunk, keep)]
-            o = _attend_rows(q[lo + t], kmat[rows], vmat[rows], H, G, D, V, scale)
-            if gate is not None:
-                o = o * torch.sigmoid(gate[lo + t].float())[:, None]
+            o = _attend_rows(q[lo + t], kmat[rows], vmat[rows], H, G, D, V, scale, softcap, sink)
+            o = _gated(o, None if gate is None else gate[lo + t], gate_wide, out_scale)
             y[lo + t] = o.reshape(-1).to(y.dtype)
     return y
 
@@ -272,10 +299,12 @@ def mma_eligible(q, kmat, vmat, y, D: int, V: int) -> bool:
 
 
 def ring_attention(q, ring, first, gate, rb, y, H: int, G: int, D: int, V: int, window: int, chunk: int, keep: int, scale: float,
-                   splits: Optional[int] = None):
+                   splits: Optional[int] = None, softcap: float = 0.0, sink: bool = False, gate_wide: bool = False,
+                   out_scale: float = 1.0):
     """Single-token steps: the same attention with keys and values read straight from ``ring`` / ``first`` (the step's own row
     has been written).  ``splits``: 0 = one warp per (token, head); n > 0 = the grouped kernel with the visible keys of a
-    (sequence, key head) cut into n parts; ``None`` chooses by the mask's reach."""
+    (sequence, key head) cut into n parts; ``None`` chooses by the mask's reach.  ``softcap``, ``sink``, ``gate_wide`` and
+    ``out_scale`` as in :func:`masked_attention`."""
     if _native(q):
         if splits is None:
             reach = (chunk if chunk > 0 else window) + keep
@@ -285,36 +314,46 @@ def ring_attention(q, ring, first, gate, rb, y, H: int, G: int, D: int, V: int, 
                 splits = max(1, min(32, (reach + 63) // 64, -(-296 // (q.shape[0] * G))))
         count_launch(1 if splits == 0 else 2)
         load_kv_ext().ring_attention(q, ring, first, gate, rb.tok_seq, rb.seq_off, rb.slots, rb.past, y, H, G, D, V, window, chunk, keep,
-                                     float(scale), splits)
+                                     float(scale), splits, float(softcap), bool(sink), bool(gate_wide), float(out_scale))
         return y
     L, nf, KC = ring.shape[1], first.shape[1], G * D
     for b in range(rb.B):
         slot, pi = rb.slot_list[b], rb.past_list[b]
         rows = torch.stack([first[slot, p] if p < nf else ring[slot, p % L] for p in _visible(pi, window, chunk, keep)])
-        o = _attend_rows(q[b], rows[:, :KC], rows[:, KC:], H, G, D, V, scale)
-        if gate is not None:
-            o = o * torch.sigmoid(gate[b].float())[:, None]
+        o = _attend_rows(q[b], rows[:, :KC], rows[:, KC:], H, G, D, V, scale, softcap, sink)
+        o = _gated(o, None if gate is None else gate[b], gate_wide, out_scale)
         y[b] = o.reshape(-1).to(y.dtype)
     return y
 
 
 # ------------------------------------------------------------------------------------------------------ mixture of experts
-def moe_route(h, wr, top: int, rscale: float, counts=None):
-    """Router: ``s = sigmoid(W_r h)`` in fp32, the ``top`` largest scores, weights ``s / (Σ s + 1e-20) · rscale``.  Returns
-    ``idx`` int32 and ``wts`` fp32, both ``[tokens, top]``; ``counts`` (int32 ``[E]``, zeroed by the caller) receives the number
-    of tokens of every expert."""
+ROUTE_SIGMOID, ROUTE_SOFTMAX = 0, 1
+
+
+def moe_route(h, wr, top: int, rscale: float, counts=None, bias=None, mode: int = ROUTE_SIGMOID):
+    """Router on the fp32 logits ``z = W_r h`` (``+ bias``, fp32 ``[E]``).  ``ROUTE_SIGMOID``: the ``top`` largest
+    ``s = sigmoid(z)``, weights ``s / (Σ s + 1e-20) · rscale``; ``ROUTE_SOFTMAX``: the ``top`` largest logits, weights = softmax
+    over the chosen logits only, times ``rscale``.  Ties go to the lower index.  Returns ``idx`` int32 and ``wts`` fp32, both
+    ``[tokens, top]``; ``counts`` (int32 ``[E]``, zeroed by the caller) receives the number of tokens of every expert."""
     T = h.shape[0]
     idx = torch.empty(T, top, dtype=torch.int32, device=h.device)
     wts = torch.empty(T, top, dtype=torch.float32, device=h.device)
     if _native(h):
         z = router_logits(h, wr)
         count_launch()
-        load_kv_ext().moe_topk(z, top, float(rscale), idx, wts, counts)
+        load_kv_ext().moe_topk(z, bias, mode, top, float(rscale), idx, wts, counts)
         return idx, wts
-    s = torch.sigmoid(F.linear(h.float(), wr.float()))
-    tv, ti = s.topk(top, -1)
+    z = F.linear(h.float(), wr.float())
+    if bias is not None:
+        z = z + bias.float()
+    if mode == ROUTE_SOFTMAX:
+        tv, ti = z.topk(top, -1)
+        w = torch.softmax(tv, -1) * rscale
+    else:
+        tv, ti = torch.sigmoid(z).topk(top, -1)
+        w = tv / (tv.sum(-1, keepdim=True) + 1e-20) * rscale
     idx.copy_(ti)
-    wts.copy_(tv / (tv.sum(-1, keepdim=True) + 1e-20) * rscale)
+    wts.copy_(w)
     if counts is not None:
         counts.add_(torch.bincount(ti.reshape(-1), minlength=counts.numel()).to(counts.dtype))
     return idx, wts
