@@ -77,9 +77,10 @@ def embed_tokens(tokens, W, emb):
 
 
 # ------------------------------------------------------------------------------------------------------------------ mixers
-def sink_window_attention(h, W, p, m):
+def sink_window_attention(h, W, p, m, window_shift=0, sink=1.0):
     """Grouped-query attention in a sliding window whose softmax has one more, value-less entry of score 0; values are the
-    keys before rotation; scores pass through a tanh cap; the heads are gated channel by channel."""
+    keys before rotation; scores pass through a tanh cap; the heads are gated channel by channel.  (``window_shift`` and ``sink``
+    exist so that a test can show that a window that is one off, or a missing sink, would be noticed.)"""
     H, G, D = m["heads"], m["kv_heads"], m["dim"]
     n = h.shape[0]
     keys, vals = [], []
@@ -90,14 +91,14 @@ def sink_window_attention(h, W, p, m):
         keys.append(torch.stack([rotate_head(k[g], t, m["rot"]) for g in range(G)]))
         q = (W[p + "q"] @ h[t]).view(H, D)
         q = torch.stack([rotate_head(q[hh], t, m["rot"]) for hh in range(H)])
-        seen = [j for j in range(t + 1) if t - j < m["mask"]["size"]]
+        seen = [j for j in range(t + 1) if t - j < m["mask"]["size"] + window_shift]
         heads = []
         for hh in range(H):
             g = hh // (H // G)
             s = torch.stack([(q[hh] * keys[j][g]).sum() * m["scale"] for j in seen])
             s = m["softcap"] * torch.tanh(s / m["softcap"])
             e = torch.exp(s)
-            pr = e / (1.0 + e.sum())
+            pr = e / (sink + e.sum())
             heads.append(sum(pj * vals[j][g] for pj, j in zip(pr, seen)))
         y = torch.cat(heads) * sigmoid(W[p + "g"] @ h[t])
         out.append(W[p + "o"] @ y)
@@ -131,8 +132,8 @@ def gated_linear_attention(h, W, p, m, eps):
     return torch.stack(out)
 
 
-def parallel_mixer(h, W, p, m, eps):
-    left = sink_window_attention(h, W, p + "left.", m["left"])
+def parallel_mixer(h, W, p, m, eps, **variant):
+    left = sink_window_attention(h, W, p + "left.", m["left"], **variant)
     right = gated_linear_attention(h, W, p + "right.", m["right"], eps)
     return m["left_scale"] * left + m["right_scale"] * right
 
@@ -167,9 +168,9 @@ def lightning_mixer(h, W, p, m, eps):
     return torch.stack(out)
 
 
-def mixer(kind, h, W, p, m, eps):
+def mixer(kind, h, W, p, m, eps, **variant):
     if kind == "parallel":
-        return parallel_mixer(h, W, p, m, eps)
+        return parallel_mixer(h, W, p, m, eps, **variant)
     if kind == "retention":
         return retention_mixer(h, W, p, m, eps)
     if kind == "lightning":
@@ -217,20 +218,28 @@ def hyper_sublayer(streams, W, p, q, fn, norm_w, eps):
     return [sum(W[f"{p}hc{q}.mix"][s, t] * streams[s] for s in range(n)) + W[f"{p}hc{q}.out"][t] * y for t in range(n)]
 
 
-def forward(cfg, W, tokens, taps=None):
+def forward(cfg, W, tokens, taps=None, **variant):
     """Logits ``[n, vocab]`` of one sequence; ``taps`` (a list) receives the sum of the streams after every block."""
+    W = as_f64(W)
     eps = cfg["norm"]["eps"]
     x = embed_tokens(tokens, W, cfg["embedding"])
     streams = [x.clone() for _ in range(cfg["streams"])]
     for i, lc in enumerate(cfg["layers"]):
         p = f"l{i}."
-        streams = hyper_sublayer(streams, W, p, 1, lambda h: mixer(lc["type"], h, W, p + "mix.", lc["mixer"], eps),
+        streams = hyper_sublayer(streams, W, p, 1, lambda h: mixer(lc["type"], h, W, p + "mix.", lc["mixer"], eps, **variant),
                                  W[p + "norm1"], eps)
         if lc.get("mlp"):
             streams = hyper_sublayer(streams, W, p, 2, lambda h: feed_forward(h, W, p + "mlp.", lc["mlp"]), W[p + "norm2"], eps)
         if taps is not None:
             taps.append(sum(streams))
     return norm_rows(sum(streams), W["final.norm"], eps) @ W["head"].t()
+
+
+def greedy(cfg, W, prompt, new_tokens):
+    seq = list(prompt)
+    for _ in range(new_tokens):
+        seq.append(int(forward(cfg, W, seq)[-1].argmax()))
+    return seq[len(prompt):]
 
 
 # ---------------------------------------------------------------------------------------------------------- configurations
