@@ -223,96 +223,294 @@ __global__ void hc_step_kernel(float* __restrict__ x, long rows, int n, int ns, 
   }
 }
 
+// The same for rows of 16-byte aligned fp32 quadruples with at most NS streams and ITEMS quadruples per thread: every load of
+// the row is issued before the first store (the streams are read and written through one pointer, so the compiler keeps the
+// program order of a load that follows a store), and u stays in registers between the two passes.
+template <typename T, typename Ty, int NS, int ITEMS>
+__global__ void hc_step_vec_kernel(float* __restrict__ x, long rows, int n, int ns, const Ty* __restrict__ y, long ldy,
+                                   const int* __restrict__ pos, const float* __restrict__ cw, int top, const float* __restrict__ mix,
+                                   const float* __restrict__ outw, const float* __restrict__ inw, const T* __restrict__ w, float eps,
+                                   T* __restrict__ h, long ldh) {
+  __shared__ float red[32];
+  const long r = blockIdx.x;
+  float cm[NS][NS], co[NS], ci[NS];
+#pragma unroll
+  for (int a = 0; a < NS; ++a) {
+    co[a] = (y && a < ns) ? outw[a] : 0.f;
+    ci[a] = (h && a < ns) ? inw[a] : 0.f;
+#pragma unroll
+    for (int b = 0; b < NS; ++b) cm[a][b] = (y && a < ns && b < ns) ? mix[a * ns + b] : 0.f;
+  }
+  float4 xs[ITEMS][NS], yv[ITEMS], uv[ITEMS];
+  int col[ITEMS];
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    col[i] = (threadIdx.x + i * blockDim.x) * 4;
+    const bool ok = col[i] < n;
+#pragma unroll
+    for (int a = 0; a < NS; ++a)
+      xs[i][a] = (ok && a < ns) ? *reinterpret_cast<const float4*>(x + ((long)a * rows + r) * n + col[i]) : make_float4(0.f, 0.f, 0.f, 0.f);
+    yv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (y && ok) {
+      if (pos) {
+        for (int k = 0; k < top; ++k) {
+          const float wk = cw[r * top + k];
+          const float4 t = ld4(y + (long)pos[r * top + k] * ldy + col[i]);
+          yv[i].x += wk * t.x; yv[i].y += wk * t.y; yv[i].z += wk * t.z; yv[i].w += wk * t.w;
+        }
+      } else {
+        yv[i] = ld4(y + r * ldy + col[i]);
+      }
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    const bool ok = col[i] < n;
+    if (y) {
+      float4 nx[NS];
+#pragma unroll
+      for (int t = 0; t < NS; ++t) {
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int q = 0; q < NS; ++q) {            // in the order of the general kernel: streams first, then the output
+          const float m = cm[q][t];
+          a.x += m * xs[i][q].x; a.y += m * xs[i][q].y; a.z += m * xs[i][q].z; a.w += m * xs[i][q].w;
+        }
+        a.x += co[t] * yv[i].x; a.y += co[t] * yv[i].y; a.z += co[t] * yv[i].z; a.w += co[t] * yv[i].w;
+        nx[t] = a;
+      }
+#pragma unroll
+      for (int t = 0; t < NS; ++t) {
+        xs[i][t] = nx[t];
+        if (ok && t < ns) *reinterpret_cast<float4*>(x + ((long)t * rows + r) * n + col[i]) = nx[t];
+      }
+    }
+    float4 u4 = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int q = 0; q < NS; ++q) { u4.x += ci[q] * xs[i][q].x; u4.y += ci[q] * xs[i][q].y; u4.z += ci[q] * xs[i][q].z; u4.w += ci[q] * xs[i][q].w; }
+    uv[i] = u4;
+    ss += u4.x * u4.x + u4.y * u4.y + u4.z * u4.z + u4.w * u4.w;
+  }
+  if (!h) return;
+  ss = block_sum(ss, red);
+  const float rr = 1.f / sqrtf(ss / (float)n + eps);
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    if (col[i] < n) {
+      const float4 wv = ld4(w + col[i]);
+      st4(h + r * ldh + col[i], make_float4(uv[i].x * rr * wv.x, uv[i].y * rr * wv.y, uv[i].z * rr * wv.z, uv[i].w * rr * wv.w));
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------------------------
 // Decayed outer-product recurrence (linear attention).  Per head, with S [D, V] in fp32:
 //   S <- diag(a_t) S + k_t v_t^T;   o_t = S^T q_t
 // a_t is one fixed number per head (`decay` [H], `z` absent) or one per key channel and token,
 // a = sigmoid(z + zb)^(inv_tau) = exp(inv_tau * log sigmoid(z + zb)) with the logits z [tokens, H*D] in fp32.
 // q, k, v are column slices of the projection output (row stride ld*); `act` 1 passes them through SiLU; q is
-// multiplied by q_scale and k by k_scale (fp32).  Columns of S are independent: a block owns `VT` of them for one
-// (sequence, head); every column is shared by R adjacent lanes that each keep DPT consecutive rows of it in registers,
-// so a token costs 3*DPT fused multiply-adds per lane and log2(R) shuffle rounds.  Tokens are staged through shared
-// memory `SCAN_CT` at a time as fp32 (rows of lane r at offset r*(DPT+4): 16-byte loads without bank conflicts), with
-// decays, activations and scales applied during staging, so the serial part only touches registers and shared memory.
+// multiplied by q_scale and k by k_scale (fp32).
+//
+// Columns of S are independent: a block owns `VT` of them for one (sequence, head).  A thread keeps a DPT x 8 tile of S
+// in registers: DPT consecutive key rows (lane r of the R = ceil(D/DPT) adjacent lanes that share a column group) of 8
+// consecutive columns, so the 2*DPT k and q numbers and 8 values a thread fetches from shared memory per token feed
+// 24*DPT fused multiply-adds: the arithmetic, not the shared-memory traffic, is the bound (a thread per column re-reads
+// k and q for every column).  The eight partial read-outs are summed over the R lanes by a transposing butterfly
+// (8 shuffles for R = 16).  Tokens are staged through shared memory CT (at most SCAN_CT) at a time as fp32 (rows of lane r at
+// a padded offset: 16-byte loads without bank conflicts) with activations, scales and decays applied during staging; the
+// global loads of the next group are issued before the serial walk over the current one and land in the other buffer
+// afterwards.
 // ------------------------------------------------------------------------------------------------------------------
-constexpr int SCAN_CT = 16;
+constexpr int SCAN_CT = 16, SCAN_NC = 8;
+
+template <typename T, int N> __device__ __forceinline__ void ldn(const T* p, float (&f)[N]);
+template <> __device__ __forceinline__ void ldn<float, 4>(const float* p, float (&f)[4]) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+}
+template <> __device__ __forceinline__ void ldn<float, 8>(const float* p, float (&f)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+template <> __device__ __forceinline__ void ldn<bf16, 4>(const bf16* p, float (&f)[4]) {
+  const float4 a = ld4(p);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+}
+template <> __device__ __forceinline__ void ldn<bf16, 8>(const bf16* p, float (&f)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { f[2 * i] = __low2float(h2[i]); f[2 * i + 1] = __high2float(h2[i]); }
+}
 
 template <typename T, int DPT>
-__global__ void __launch_bounds__(256, DPT <= 16 ? 2 : 1)
+__global__ void __launch_bounds__(256, 1)
 decay_scan_kernel(const T* __restrict__ q, long ldq, const T* __restrict__ k, long ldk, const T* __restrict__ v, long ldv,
                   const float* __restrict__ decay, const float* __restrict__ z, long ldz, const float* __restrict__ zb, float inv_tau,
                   float q_scale, float k_scale, int act, float* __restrict__ S, const int* __restrict__ seq_off,
                   const int* __restrict__ slots, const int* __restrict__ past, float* __restrict__ out, int H, int D, int V, int R,
-                  int VT) {
+                  int VT, int CT, int vec) {
   extern __shared__ __align__(16) float sm[];
-  constexpr int PS = DPT + 4;                   // padded stride of one lane's rows
+  constexpr int NC = SCAN_NC, PS = DPT == 8 ? 12 : 4;   // padded stride of one lane's rows
   const int b = blockIdx.x / H, h = blockIdx.x % H;
   const int j0 = blockIdx.y * VT;
-  const int Dr = R * DPT;                       // rows covered (rows >= D hold zeros)
   const int Dp = R * PS;                        // floats per staged token
   const bool chan = z != nullptr;
-  float* sk = sm;                               // [CT][Dp]
-  float* sq = sk + SCAN_CT * Dp;                // [CT][Dp]
-  float* sg = sq + SCAN_CT * Dp;                // [CT][Dp] (chan) or nothing
-  float* sv = sg + (chan ? SCAN_CT * Dp : 0);   // [CT][VT]
+  const int buf_floats = CT * (Dp * (chan ? 3 : 2) + VT);
   const int tid = threadIdx.x, nth = blockDim.x;
-  const int r = tid % R, jj = tid / R, j = j0 + jj;
-  const bool col_ok = jj < VT && j < V;
+  const int r = tid % R, grp = tid / R;         // lane within the column group, column group
+  const int jc = j0 + grp * NC;                 // first of this thread's 8 columns
+  const bool grp_ok = grp * NC < VT;
   const int n = seq_off[b + 1] - seq_off[b];
   const long tok0 = seq_off[b];
   const float g0 = chan ? 1.f : decay[h];
   float* Sg = S + ((long)slots[b] * H + h) * (long)D * V;
-  float s[DPT];
+  float s[DPT][NC];
 #pragma unroll
   for (int d = 0; d < DPT; ++d) {
     const int i = r * DPT + d;
-    s[d] = (past[b] > 0 && col_ok && i < D) ? Sg[(long)i * V + j] : 0.f;
+#pragma unroll
+    for (int c = 0; c < NC; ++c) s[d][c] = (past[b] > 0 && grp_ok && i < D && jc + c < V) ? Sg[(long)i * V + jc + c] : 0.f;
   }
-  for (int c0 = 0; c0 < n; c0 += SCAN_CT) {
-    const int ct = min(SCAN_CT, n - c0);
-    __syncthreads();
-    for (int e = tid; e < ct * Dr; e += nth) {
-      const int t = e / Dr, i = e - t * Dr;
-      const int at = t * Dp + (i / DPT) * PS + (i % DPT);
+  // staging work of this thread: one (token, lane chunk) of q / k / decays and one (token, column group) of v per group of CT
+  // tokens (the launcher picks CT so that both fit the block)
+  const int qk_items = CT * R, v_items = CT * (VT / NC);
+  float rk[DPT], rq[DPT], rg[DPT], rv[NC];
+  auto fetch = [&](int c0) {                    // global loads of the group that starts at token c0, into registers
+    const int ct = min(CT, n - c0);
+    if (tid < qk_items) {
+      const int t = tid / R, rr = tid - t * R;
       const long row = tok0 + c0 + t;
-      const bool in = i < D;
-      float kv = in ? ldf(k + row * ldk + h * D + i) : 0.f, qv = in ? ldf(q + row * ldq + h * D + i) : 0.f;
-      if (act) { kv = siluf_(kv); qv = siluf_(qv); }
-      sk[at] = kv * k_scale;
-      sq[at] = qv * q_scale;
-      if (chan) sg[at] = in ? expf(inv_tau * logsigmoidf_(z[row * ldz + h * D + i] + zb[h * D + i])) : 1.f;
+      const int i0 = rr * DPT;
+      if (t < ct && vec && i0 + DPT <= D) {
+        ldn<T, DPT>(k + row * ldk + h * D + i0, rk);
+        ldn<T, DPT>(q + row * ldq + h * D + i0, rq);
+        if (chan) {
+          ldn<float, DPT>(z + row * ldz + h * D + i0, rg);
+          float bb[DPT];
+          ldn<float, DPT>(zb + h * D + i0, bb);
+#pragma unroll
+          for (int d = 0; d < DPT; ++d) rg[d] += bb[d];
+        }
+      } else {
+#pragma unroll
+        for (int d = 0; d < DPT; ++d) {
+          const bool in = t < ct && i0 + d < D;
+          rk[d] = in ? ldf(k + row * ldk + h * D + i0 + d) : 0.f;
+          rq[d] = in ? ldf(q + row * ldq + h * D + i0 + d) : 0.f;
+          if (chan) rg[d] = in ? z[row * ldz + h * D + i0 + d] + zb[h * D + i0 + d] : 1e30f;   // sigmoid(huge) = 1: no decay
+        }
+      }
     }
-    for (int e = tid; e < ct * VT; e += nth) {
-      const int t = e / VT, c = e - t * VT;
-      float vv = (j0 + c < V) ? ldf(v + (tok0 + c0 + t) * ldv + h * V + j0 + c) : 0.f;
-      if (act) vv = siluf_(vv);
-      sv[e] = vv;
+    if (tid < v_items) {
+      const int t = tid / (VT / NC), cg = tid - t * (VT / NC);
+      const long row = tok0 + c0 + t;
+      const int col = j0 + cg * NC;
+      if (t < ct && vec && col + NC <= V) {
+        ldn<T, NC>(v + row * ldv + h * V + col, rv);
+      } else {
+#pragma unroll
+        for (int c = 0; c < NC; ++c) rv[c] = (t < ct && col + c < V) ? ldf(v + row * ldv + h * V + col + c) : 0.f;
+      }
     }
-    __syncthreads();
-    // every thread walks the tokens (lanes of idle columns included: the shuffles below name the whole warp)
-    for (int t = 0; t < ct; ++t) {
-      float pq[4] = {0.f, 0.f, 0.f, 0.f};
-      const float4* k4 = reinterpret_cast<const float4*>(sk + t * Dp + r * PS);
-      const float4* q4 = reinterpret_cast<const float4*>(sq + t * Dp + r * PS);
-      const float4* g4 = reinterpret_cast<const float4*>(sg + t * Dp + r * PS);
-      const float vt = jj < VT ? sv[t * VT + jj] : 0.f;
+  };
+  auto stash = [&](float* buf) {                // registers -> shared memory, with activations, scales and decays applied
+    float* sk = buf; float* sq = sk + CT * Dp; float* sg = sq + CT * Dp; float* sv = sg + (chan ? CT * Dp : 0);
+    if (tid < qk_items) {
+      const int t = tid / R, rr = tid - t * R;
+      float ko[DPT], qo[DPT], go[DPT];
+#pragma unroll
+      for (int d = 0; d < DPT; ++d) {
+        float kv = rk[d], qv = rq[d];
+        if (act) { kv = siluf_(kv); qv = siluf_(qv); }
+        ko[d] = kv * k_scale; qo[d] = qv * q_scale;
+        go[d] = chan ? expf(inv_tau * logsigmoidf_(rg[d])) : 1.f;
+      }
 #pragma unroll
       for (int d4 = 0; d4 < DPT / 4; ++d4) {
-        const float4 kx = k4[d4], qx = q4[d4];
-        float4 gx = make_float4(g0, g0, g0, g0);
-        if (chan) gx = g4[d4];
-        s[4 * d4] = s[4 * d4] * gx.x + kx.x * vt; s[4 * d4 + 1] = s[4 * d4 + 1] * gx.y + kx.y * vt;
-        s[4 * d4 + 2] = s[4 * d4 + 2] * gx.z + kx.z * vt; s[4 * d4 + 3] = s[4 * d4 + 3] * gx.w + kx.w * vt;
-        pq[0] += s[4 * d4] * qx.x; pq[1] += s[4 * d4 + 1] * qx.y; pq[2] += s[4 * d4 + 2] * qx.z; pq[3] += s[4 * d4 + 3] * qx.w;
+        reinterpret_cast<float4*>(sk + t * Dp + rr * PS)[d4] = make_float4(ko[4 * d4], ko[4 * d4 + 1], ko[4 * d4 + 2], ko[4 * d4 + 3]);
+        reinterpret_cast<float4*>(sq + t * Dp + rr * PS)[d4] = make_float4(qo[4 * d4], qo[4 * d4 + 1], qo[4 * d4 + 2], qo[4 * d4 + 3]);
+        if (chan) reinterpret_cast<float4*>(sg + t * Dp + rr * PS)[d4] = make_float4(go[4 * d4], go[4 * d4 + 1], go[4 * d4 + 2], go[4 * d4 + 3]);
       }
-      float o = (pq[0] + pq[1]) + (pq[2] + pq[3]);
-      for (int m = R >> 1; m > 0; m >>= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
-      if (r == 0 && col_ok) out[(tok0 + c0 + t) * (long)(H * V) + h * V + j] = o;
     }
-  }
-  if (col_ok) {
+    if (tid < v_items) {
+      float vo[NC];
 #pragma unroll
-    for (int d = 0; d < DPT; ++d) { const int i = r * DPT + d; if (i < D) Sg[(long)i * V + j] = s[d]; }
+      for (int c = 0; c < NC; ++c) vo[c] = act ? siluf_(rv[c]) : rv[c];
+      reinterpret_cast<float4*>(sv)[2 * tid] = make_float4(vo[0], vo[1], vo[2], vo[3]);
+      reinterpret_cast<float4*>(sv)[2 * tid + 1] = make_float4(vo[4], vo[5], vo[6], vo[7]);
+    }
+  };
+  fetch(0);
+  stash(sm);
+  __syncthreads();
+  int cur = 0;
+  for (int c0 = 0; c0 < n; c0 += CT) {
+    const int ct = min(CT, n - c0);
+    const bool more = c0 + CT < n;
+    if (more) fetch(c0 + CT);                   // in flight during the serial walk below
+    const float* buf = sm + cur * buf_floats;
+    const float* sk = buf + r * PS; const float* sq = sk + CT * Dp; const float* sg = sq + CT * Dp;
+    const float* sv = buf + CT * Dp * (chan ? 3 : 2) + (grp_ok ? grp * NC : 0);
+    float* orow = out + (tok0 + c0) * (long)(H * V) + h * V;
+    // every thread walks the tokens (lanes of idle column groups included: the shuffles below name the whole warp)
+#pragma unroll 2
+    for (int t = 0; t < ct; ++t, sk += Dp, sq += Dp, sg += Dp, sv += VT, orow += H * V) {
+      const float4 va = reinterpret_cast<const float4*>(sv)[0], vb = reinterpret_cast<const float4*>(sv)[1];
+      const float vt[NC] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+      float o[NC];
+#pragma unroll
+      for (int c = 0; c < NC; ++c) o[c] = 0.f;
+#pragma unroll
+      for (int d4 = 0; d4 < DPT / 4; ++d4) {
+        const float4 kx = reinterpret_cast<const float4*>(sk)[d4], qx = reinterpret_cast<const float4*>(sq)[d4];
+        float4 gx = make_float4(g0, g0, g0, g0);
+        if (chan) gx = reinterpret_cast<const float4*>(sg)[d4];
+        const float kk[4] = {kx.x, kx.y, kx.z, kx.w}, qq[4] = {qx.x, qx.y, qx.z, qx.w}, gg[4] = {gx.x, gx.y, gx.z, gx.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+#pragma unroll
+          for (int c = 0; c < NC; ++c) {
+            s[4 * d4 + e][c] = s[4 * d4 + e][c] * gg[e] + kk[e] * vt[c];
+            o[c] += s[4 * d4 + e][c] * qq[e];
+          }
+        }
+      }
+      if (R >= 8) {
+        // transposing butterfly: after three rounds a lane holds, for one column, the sum over its 8 neighbouring lanes
+        const bool b0 = r & 1, b1 = r & 2, b2 = r & 4;
+        float a[4], bq[2];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) a[i] = (b0 ? o[4 + i] : o[i]) + __shfl_xor_sync(0xffffffffu, b0 ? o[i] : o[4 + i], 1);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) bq[i] = (b1 ? a[2 + i] : a[i]) + __shfl_xor_sync(0xffffffffu, b1 ? a[i] : a[2 + i], 2);
+        float w = (b2 ? bq[1] : bq[0]) + __shfl_xor_sync(0xffffffffu, b2 ? bq[0] : bq[1], 4);
+        for (int m = 8; m < R; m <<= 1) w += __shfl_xor_sync(0xffffffffu, w, m);
+        const int col = jc + (b0 ? 4 : 0) + (b1 ? 2 : 0) + (b2 ? 1 : 0);
+        if (r < 8 && grp_ok && col < V) orow[col] = w;
+      } else {
+        for (int m = R >> 1; m > 0; m >>= 1) {
+#pragma unroll
+          for (int c = 0; c < NC; ++c) o[c] += __shfl_xor_sync(0xffffffffu, o[c], m);
+        }
+        if (r == 0 && grp_ok) {
+#pragma unroll
+          for (int c = 0; c < NC; ++c) if (jc + c < V) orow[jc + c] = o[c];
+        }
+      }
+    }
+    if (more) stash(sm + (cur ^ 1) * buf_floats);
+    __syncthreads();                            // the other buffer is complete, and nobody reads this one any more
+    cur ^= 1;
+  }
+  if (grp_ok) {
+#pragma unroll
+    for (int d = 0; d < DPT; ++d) {
+      const int i = r * DPT + d;
+#pragma unroll
+      for (int c = 0; c < NC; ++c) if (i < D && jc + c < V) Sg[(long)i * V + jc + c] = s[d][c];
+    }
   }
 }
 
@@ -390,6 +588,22 @@ int lbl_hc_step(float* x, long rows, int n, int ns, const void* y, long ldy, int
   int vec = (n % 4 == 0 && ((uintptr_t)x & 15) == 0) ? 1 : 0;
   if (y && (((uintptr_t)y & 15) != 0 || ldy % 4 != 0)) vec = 0;
   if (h && (((uintptr_t)h & 15) != 0 || ldh % 4 != 0 || ((uintptr_t)w & 15) != 0)) vec = 0;
+  const int quads = n / 4;
+  if (vec && ns <= 4 && quads <= 2048) {          // every quadruple of the row in registers: at most two per thread
+    const int items = quads <= 128 ? 1 : 2;
+    const int vthreads = (((quads + items - 1) / items + 31) / 32) * 32;
+    const int nsb = ns <= 1 ? 1 : (ns <= 2 ? 2 : 4);
+#define HCV3(TT, TY, NSB, IT) hc_step_vec_kernel<TT, TY, NSB, IT><<<(unsigned)rows, vthreads, 0, s>>>(x, rows, n, ns, (const TY*)y, ldy, pos, cw, \
+        top, mix, outw, inw, (const TT*)w, eps, (TT*)h, ldh)
+#define HCV2(TT, TY, NSB) { if (items == 1) HCV3(TT, TY, NSB, 1); else HCV3(TT, TY, NSB, 2); }
+#define HCV(TT, TY) { if (nsb == 1) HCV2(TT, TY, 1) else if (nsb == 2) HCV2(TT, TY, 2) else HCV2(TT, TY, 4) }
+    if (dtype) { if (ydtype) HCV(bf16, bf16) else HCV(bf16, float) }
+    else { if (ydtype) return -1; HCV(float, float) }
+#undef HCV
+#undef HCV2
+#undef HCV3
+    LAUNCH_END();
+  }
   const int threads = n >= 2048 ? 256 : 128;
 #define HC(TT, TY) { \
     if (smem > 48 * 1024) cudaFuncSetAttribute(hc_step_kernel<TT, TY>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
@@ -406,21 +620,31 @@ int lbl_decay_scan(const void* q, long ldq, const void* k, long ldk, const void*
                    const int* slots, const int* past, float* out, int B, int H, int D, int V, int dtype, cudaStream_t s) {
   if (B == 0) return 0;
   if (D > 256 || (!decay && !z) || (z && !zb)) return -1;
-  const int dpt = D <= 32 ? 8 : (D <= 128 ? 16 : 32);  // rows per lane: 4 lanes per column up to D = 64, 8 lanes up to 256
+  const int dpt = D <= 64 ? 4 : 8;              // rows per lane: 16 lanes per column group at D = 64 and at D = 128
   int R = 1;
-  while (R * dpt < D) R <<= 1;                   // a power of two <= 8
-  int VT = R <= 4 ? 64 : 32;                     // columns per block (columns are independent: more blocks per head)
-  if (V < VT) VT = V;
-  const int threads = ((VT * R + 31) / 32) * 32;
-  const int Dp = R * (dpt + 4);
-  const size_t smem = sizeof(float) * ((size_t)SCAN_CT * Dp * (z ? 3 : 2) + (size_t)SCAN_CT * VT);
+  while (R * dpt < D) R <<= 1;                  // lanes per column group: a power of two <= 32
+  const int groups_max = 256 / R;               // column groups of 8 columns in a block of 256 threads
+  int groups = (V + SCAN_NC - 1) / SCAN_NC;
+  if (groups > groups_max) groups = groups_max;
+  // columns are independent: smaller blocks when one block per (sequence, head) would leave most SMs idle
+  while (groups > 2 && groups % 2 == 0 && (long)B * H * ((V + groups * SCAN_NC - 1) / (groups * SCAN_NC)) < 100) groups /= 2;
+  const int VT = groups * SCAN_NC;
+  const int threads = ((groups * R + 31) / 32) * 32;
+  int CT = SCAN_CT;                             // tokens per staged group: one (token, lane chunk) and one (token, column group) per thread
+  while (CT > 1 && (CT * R > threads || CT * groups > threads)) CT >>= 1;
+  const int Dp = R * (dpt == 8 ? 12 : 4);
+  const size_t smem = 2 * sizeof(float) * (size_t)CT * ((size_t)Dp * (z ? 3 : 2) + VT);
   const dim3 grid((unsigned)(B * H), (unsigned)((V + VT - 1) / VT));
+  const int esz = dtype ? 2 : 4;
+  const int vec = (D % 8 == 0 && V % 8 == 0 && (ldq * esz) % 16 == 0 && (ldk * esz) % 16 == 0 && (ldv * esz) % 16 == 0 &&
+                   ((uintptr_t)q & 15) == 0 && ((uintptr_t)k & 15) == 0 && ((uintptr_t)v & 15) == 0 &&
+                   (!z || (ldz % 4 == 0 && ((uintptr_t)z & 15) == 0 && ((uintptr_t)zb & 15) == 0))) ? 1 : 0;
 #define DS(TT, P) { \
     if (smem > 48 * 1024) cudaFuncSetAttribute(decay_scan_kernel<TT, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     decay_scan_kernel<TT, P><<<grid, threads, smem, s>>>((const TT*)q, ldq, (const TT*)k, ldk, (const TT*)v, ldv, decay, z, ldz, zb, \
-        inv_tau, q_scale, k_scale, act, S, seq_off, slots, past, out, H, D, V, R, VT); }
-  if (dtype == 0) { if (dpt == 8) DS(float, 8) else if (dpt == 16) DS(float, 16) else DS(float, 32) }
-  else { if (dpt == 8) DS(bf16, 8) else if (dpt == 16) DS(bf16, 16) else DS(bf16, 32) }
+        inv_tau, q_scale, k_scale, act, S, seq_off, slots, past, out, H, D, V, R, VT, CT, vec); }
+  if (dtype == 0) { if (dpt == 4) DS(float, 4) else DS(float, 8) }
+  else { if (dpt == 4) DS(bf16, 4) else DS(bf16, 8) }
 #undef DS
   LAUNCH_END();
 }

@@ -1,7 +1,8 @@
 """Prefill / decode throughput of the stateful models (Bumodra: delta-rule and latent-attention mixers; Nefelorn: ring-cached
 attention with chunk / kept-first window masks and mixture-of-experts feed-forwards) beside Llama at equal width, depth and
-(active) feed-forward size, random weights, one GPU.  ``bench.py --serving [--serving-model nefelorn]`` prints the result as
-one JSON line; ``--serving-kernels`` adds device times of the individual kernels of one block at the same sizes with their
+(active) feed-forward size, and of Salizen (hyper-connection streams, linear-attention recurrences, sink-softmax window
+attention) beside Nefelorn, random weights, one GPU.  ``bench.py --serving [--serving-model nefelorn|salizen]`` prints the result
+as one JSON line; ``--serving-kernels`` adds device times of the individual kernels of one block at the same sizes with their
 roofline fractions.
 
 Timing: CUDA events on the launching stream after warm-up steps, a synchronize on both sides, an L2 flush (a write larger
@@ -380,11 +381,202 @@ def kernel_table_nefelorn(s, batch, prompt):
     return {"peaks": src, "hbm_bytes_per_s": hbm, "bf16_flops": flops, "rows": rows}
 
 
+# ======================================================================================================================
+# Salizen beside Nefelorn (the framework's closest model: ring-cached window attention, experts, the same scheduler)
+# ======================================================================================================================
+def salizen_config(s):
+    """The sizes of :data:`NEFELORN_SIZES`: the attention side of the parallel block has Nefelorn's heads and reach, the
+    recurrences have as many heads of the same size, dense and expert feed-forwards have Nefelorn's sizes."""
+    D, H = s["dim"], s["heads"]
+    moe = {"kind": "moe", "expert": {"ff": s["expert_ff"]}, "router": {"experts": s["experts"], "top": s["top"]}}
+    left = {"heads": H, "kv_heads": s["kv_heads"], "dim": D, "vdim": D, "mask": {"size": s["reach"]}, "scale": D ** -0.5, "softcap": 50.0,
+            "rot": {"dims": D // 2, "base": 500000.0, "scaling": {"factor": 4.0, "original": 4096, "low": 1.0, "high": 4.0}}}
+    right = {"heads": H, "dim": D // 2, "vdim": D, "tau": 16.0, "decay_rank": 64}
+    decay = [1.0 - 2.0 ** (-3 - (i % 8)) for i in range(H)]
+    kinds = [{"type": "parallel", "mlp": {"kind": "dense", "ff": s["ff"]},
+              "mixer": {"left": left, "right": right, "left_scale": 0.8, "right_scale": 0.5}},
+             {"type": "retention", "mlp": moe, "mixer": {"heads": H, "dim": D, "vdim": D, "decay": decay, "rot": {"dims": D, "base": 10000.0}}},
+             {"type": "lightning", "mlp": moe, "mixer": {"heads": H, "dim": D, "vdim": D, "decay": decay}},
+             {"type": "lightning", "mlp": moe, "mixer": {"heads": H, "dim": D, "vdim": D, "decay": decay}}]
+    return dict(vocab=s["vocab"], width=s["width"], streams=2, norm={"eps": 1e-6},
+                embedding={"scale": s["width"] ** 0.5, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}},
+                layers=[json.loads(json.dumps(kinds[i % 4])) for i in range(s["blocks"])])
+
+
+def _stateful_throughput(model, name, ids, batch, new_tokens, steps, warmup, out):
+    """Prefill (one ragged step for all prompts) and single-token steps (graph replay, and eager launches) through the scheduler."""
+    from libai_b200.inference.scheduler import RequestScheduler
+
+    sched = RequestScheduler(model)
+    prompts = [row.tolist() for row in ids]
+
+    def prefill():
+        sched.step([(("p", i), p, [len(p) - 1]) for i, p in enumerate(prompts)])
+        sched.finish([("p", i) for i in range(batch)])
+
+    out[f"{name}_prefill_ms"] = _time(prefill, warmup, steps)
+    sched.step([(("d", i), p, []) for i, p in enumerate(prompts)])
+    entries = [(("d", i), [7], [0]) for i in range(batch)]
+    out[f"{name}_decode_ms"] = _time(lambda: sched.step(entries), warmup, new_tokens)
+    sched.cuda_graphs = False
+    out[f"{name}_decode_eager_ms"] = _time(lambda: sched.step(entries), warmup, new_tokens)
+    sched.finish([("d", i) for i in range(batch)])
+    out[f"{name}_prefill_tokens_per_s"] = batch * ids.shape[1] / out[f"{name}_prefill_ms"] * 1e3
+    out[f"{name}_decode_tokens_per_s"] = batch / out[f"{name}_decode_ms"] * 1e3
+    out[f"params_{name}"] = sum(p.numel() for p in model.parameters())
+
+
+@torch.no_grad()
+def throughput_salizen(s, batch, prompt, new_tokens, steps, warmup):
+    from libai_b200.config import DictConfig
+    from libai_b200.layers._param import param_defaults
+    from libai_b200.models import NefelornForCausalLM, SalizenForCausalLM
+
+    ids = torch.randint(1, s["vocab"], (batch, prompt), generator=torch.Generator().manual_seed(0))
+    out = {}
+    for name, cls, cfg in (("salizen", SalizenForCausalLM, salizen_config(s)), ("nefelorn", NefelornForCausalLM, nefelorn_config(s))):
+        with param_defaults(dtype=torch.bfloat16, device="cuda", seed=1):
+            model = cls(DictConfig(cfg)).eval().cuda()
+        _stateful_throughput(model, name, ids, batch, new_tokens, steps, warmup, out)
+        del model
+        torch.cuda.empty_cache()
+    return out
+
+
+@torch.no_grad()
+def kernel_table_salizen(s, batch, prompt):
+    """Device time of every kernel of a Salizen block at these sizes (prefill rows = batch·prompt; decode rows = batch) beside the
+    like kernel of Nefelorn (or, for the recurrence, of Bumodra), with the bytes / FLOPs the operation needs and the fraction of
+    the measured roofline."""
+    from libai_b200.inference.ragged import RaggedBatch
+    from libai_b200.layers import DynamicTanh
+    from libai_b200.layers._param import param_defaults
+    from libai_b200.ops import kv_functional as KF
+    from libai_b200.ops import lin_functional as LF
+    from libai_b200.ops import seq_functional as SF
+
+    hbm, flops, src = _peaks()
+    dev, bf = "cuda", torch.bfloat16
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    n, H, G, D, R = s["width"], s["heads"], s["kv_heads"], s["dim"], s["reach"]
+    E, top, S = s["experts"], s["top"], 2
+    C = G * 2 * D
+    rows = []
+
+    def add(name, ms, bytes_=0.0, fl=0.0):
+        ideal = max(bytes_ / hbm, fl / flops) * 1e3
+        rows.append(dict(kernel=name, ms=round(ms, 4), ideal_ms=round(ideal, 5), roofline_fraction=round(ideal / ms, 4),
+                         bound="memory" if bytes_ / hbm >= fl / flops else "tensor"))
+
+    with param_defaults(dtype=bf, device=dev, seed=2):
+        na, nb = DynamicTanh(n), DynamicTanh(n)
+    mix, outw, inw = torch.eye(S, device=dev) * 0.9 + 0.05, torch.ones(S, device=dev), torch.ones(S, device=dev) * 0.5
+    table = torch.randn(s["vocab"], n, device=dev).to(bf)
+    bigram = torch.randn(65522, n, device=dev).to(bf)
+    for phase, lens, past in (("prefill", [prompt] * batch, [0] * batch), ("decode", [1] * batch, [prompt] * batch)):
+        rb = RaggedBatch(lens, list(range(batch)), past, dev)
+        T = rb.tokens
+        ids = torch.randint(0, s["vocab"], (T,), device=dev)
+        last = torch.zeros(batch, dtype=torch.int32, device=dev)
+        xs = torch.randn(S, T, n, device=dev)
+        add(f"{phase}: token + bigram embedding into {S} streams", _time(lambda: LF.embed_bigram(table, bigram, ids, last, rb, 30.0, 31, 17, 65521, xs), flush=flush),
+            T * n * (4 + 4 * S))
+        x1 = torch.randn(T, n, device=dev)
+        add(f"{phase}: Nefelorn embedding", _time(lambda: KF.embed_scale(table, ids, 30.0, x1), flush=flush), T * n * 6)
+        y32 = torch.randn(T, n, device=dev)
+        h = torch.empty(T, n, dtype=bf, device=dev)
+        w = torch.ones(n, dtype=bf, device=dev)
+        add(f"{phase}: stream write-back + read + RMS norm ({S} streams)",
+            _time(lambda: LF.hc_step(xs, y32, post=(mix, outw), nxt=(inw, w), h=h, eps=1e-6), flush=flush), T * n * (8 * S + 6))
+        add(f"{phase}: Nefelorn closing norm + residual + opening norm (one stream)",
+            _time(lambda: KF.dyt_residual(x1, y32, post=na.triple(), nxt=nb.triple(), h=h), flush=flush), T * n * 14)
+        # attention side: rotation, cache write, attention with cap + sink + channel gate beside the same kernel without them
+        q = torch.randn(T, H * D, device=dev).to(bf)
+        kv = torch.randn(T, C, device=dev).to(bf)
+        freq, ms_ = KF.rotary_frequencies(D // 2, 5e5, {"factor": 4.0, "original": 4096, "low": 1.0, "high": 4.0})
+        freq = freq.to(dev)
+        add(f"{phase}: rotation of queries and keys", _time(lambda: KF.qk_prepare(q, kv[:, :G * D], None, None, freq, ms_, rb, H, G, D, 1e-6, False, False), flush=flush),
+            T * (H + G) * D * 4)
+        ring = torch.randn(batch, R, C, device=dev).to(bf)
+        first = torch.zeros(batch, 0, C, dtype=bf, device=dev)
+        wide, narrow = torch.randn(T, H * D, device=dev).to(bf), torch.randn(T, H, device=dev).to(bf)
+        yb = torch.empty(T, H * D, dtype=bf, device=dev)
+        extra = dict(softcap=50.0, sink=True, gate_wide=True, out_scale=0.8)
+        if phase == "prefill":
+            ext = rb.kv_ext([(R, 0, 0)])
+            pairs = sum(min(t + 1, R) for t in range(prompt)) * batch
+            add("prefill: window attention with score cap, sink and channel gate (mma.sync)",
+                _time(lambda: KF.masked_attention(q, kv[:, :G * D], kv[:, G * D:], ext, wide, rb, yb, H, G, D, D, R, 0, 0, D ** -0.5, **extra), flush=flush),
+                T * H * D * 6 + T * C * 2, pairs * H * D * 4.0)
+            add("prefill: Nefelorn window attention with head gate (same kernel without them)",
+                _time(lambda: KF.masked_attention(q, kv[:, :G * D], kv[:, G * D:], ext, narrow, rb, yb, H, G, D, D, R, 0, 0, D ** -0.5), flush=flush),
+                T * H * D * 4 + T * C * 2, pairs * H * D * 4.0)
+        else:
+            add("decode: grouped ring attention with score cap, sink and channel gate",
+                _time(lambda: KF.ring_attention(q, ring, first, wide, rb, yb, H, G, D, D, R, 0, 0, D ** -0.5, **extra), flush=flush),
+                batch * min(prompt + 1, R) * C * 2)
+            add("decode: Nefelorn grouped ring attention (same kernel without them)",
+                _time(lambda: KF.ring_attention(q, ring, first, narrow, rb, yb, H, G, D, D, R, 0, 0, D ** -0.5), flush=flush),
+                batch * min(prompt + 1, R) * C * 2)
+        # recurrences: fixed decay per head (retention / lightning), decay logits per key channel (gated linear attention)
+        k2, v2 = torch.randn(T, H * D, device=dev).to(bf), torch.randn(T, H * D, device=dev).to(bf)
+        St = torch.zeros(batch, H, D, D, device=dev)
+        decay = torch.full((H,), 0.97, device=dev)
+        state_bytes = batch * H * D * D * 4 * (2 if phase == "decode" else 1)
+        fma = T * H * D * D * 2.0                                    # state update + read-out, fused multiply-adds
+        add(f"{phase}: decay scan, one decay per head (state {D} x {D})",
+            _time(lambda: LF.decay_scan(q, k2, v2, St, rb, decay=decay, k_scale=D ** -0.5), flush=flush), T * H * D * (6 + 4) + state_bytes)
+        rows[-1]["fp32_fma"] = fma
+        add(f"{phase}: decay scan with SiLU on q, k, v", _time(lambda: LF.decay_scan(q, k2, v2, St, rb, decay=decay, act=True), flush=flush),
+            T * H * D * (6 + 4) + state_bytes)
+        Dg = D // 2
+        qg, kg = torch.randn(T, H * Dg, device=dev).to(bf), torch.randn(T, H * Dg, device=dev).to(bf)
+        z, zb = torch.randn(T, H * Dg, device=dev), torch.randn(H * Dg, device=dev) + 2.0
+        Sg = torch.zeros(batch, H, Dg, D, device=dev)
+        add(f"{phase}: decay scan, decay logits per key channel (state {Dg} x {D})",
+            _time(lambda: LF.decay_scan(qg, kg, v2, Sg, rb, z=z, zb=zb, tau=16.0, q_scale=Dg ** -0.5), flush=flush),
+            T * H * (Dg * 8 + D * 6) + state_bytes // 2)
+        KH = H // 2
+        Cq = 2 * KH * D + H * D
+        conv = torch.randn(T, Cq, device=dev).to(bf)
+        a, b = torch.randn(T, H, device=dev).to(bf), torch.randn(T, H, device=dev).to(bf)
+        A_log, dtb = torch.zeros(H, dtype=bf, device=dev), torch.zeros(H, dtype=bf, device=dev)
+        add(f"{phase}: Bumodra delta scan (per-head decay, state {D} x {D})",
+            _time(lambda: SF.delta_scan(conv, KH * D, 2 * KH * D, a, b, A_log, dtb, St, rb, KH, False), flush=flush),
+            T * (Cq * 2 + H * D * 4) + state_bytes)
+        o = torch.randn(T, H * D, device=dev)
+        nw, nall = torch.ones(D, dtype=bf, device=dev), torch.ones(H * D, dtype=bf, device=dev)
+        add(f"{phase}: gated RMS norm per head", _time(lambda: LF.gated_norm(o, wide, nw, 1e-6, LF.GATE_SILU, yb, H, D, per_head=True), flush=flush), T * H * D * 8)
+        add(f"{phase}: gated RMS norm over all heads", _time(lambda: LF.gated_norm(o, wide, nall, 1e-6, LF.GATE_SIGMOID, yb, H, D, per_head=False), flush=flush),
+            T * H * D * 8)
+        add(f"{phase}: Bumodra gated RMS norm per head", _time(lambda: SF.gated_rmsnorm(o, wide, nw, 1e-6, 0, yb, H, D), flush=flush), T * H * D * 8)
+        hb = torch.randn(T, n, device=dev).to(bf)
+        wr, rbias = torch.randn(E, n, device=dev).to(bf), torch.randn(E, device=dev)
+        add(f"{phase}: router (bias, softmax over the top-{top} of {E})",
+            _time(lambda: KF.moe_route(hb, wr, top, 1.0, bias=rbias, mode=KF.ROUTE_SOFTMAX), flush=flush), T * n * 2 + E * n * 2)
+        add(f"{phase}: Nefelorn router (sigmoid)", _time(lambda: KF.moe_route(hb, wr, top, 1.0), flush=flush), T * n * 2 + E * n * 2)
+    return {"peaks": src, "hbm_bytes_per_s": hbm, "bf16_flops": flops, "rows": rows}
+
+
 def main(args):
     assert torch.cuda.is_available(), "the serving bench needs a GPU"
     from libai_b200 import ops
 
     ops.reset_launch_count()
+    if getattr(args, "serving_model", "bumodra") == "salizen":
+        result = {"metric": "prefill / decode tokens per second, Salizen beside Nefelorn at equal width, depth, heads and active feed-forward size",
+                  "dtype": "bf16", "data": "synthetic tokens, random-init weights", "n_gpus": 1, "sizes": {}}
+        for name in (args.serving_sizes.split(",") if args.serving_sizes else list(NEFELORN_SIZES)):
+            s = NEFELORN_SIZES[name]
+            r = throughput_salizen(s, args.serving_batch, args.serving_prompt, new_tokens=max(args.steps, 8),
+                                   steps=max(args.steps // 2, 3), warmup=max(args.warmup, 3))
+            if args.serving_kernels:
+                r["kernels"] = kernel_table_salizen(s, args.serving_batch, args.serving_prompt)
+            result["sizes"][name] = {"config": dict(s), "batch": args.serving_batch, "prompt": args.serving_prompt, **r}
+            torch.cuda.empty_cache()
+        result["gpu_launches"] = ops.launch_count()
+        print(json.dumps(result))
+        return
     if getattr(args, "serving_model", "bumodra") == "nefelorn":
         result = {"metric": "prefill / decode tokens per second, Nefelorn beside Llama at equal width, depth and active feed-forward size",
                   "dtype": "bf16", "data": "synthetic tokens, random-init weights", "n_gpus": 1, "sizes": {}}
