@@ -1,7 +1,7 @@
-"""Run prefill or single-token steps of a random-weight Nefelorn model of one of the serving-bench sizes — a small, Nefelorn-only
-workload for a profiler (launch lists, captures of one kernel):
+"""Run prefill or single-token steps of a random-weight Nefelorn (or, ``--model salizen``, Salizen) model of one of the
+serving-bench sizes — a small, one-model workload for a profiler (launch lists, captures of one kernel):
 
-    python dev/nefelorn_step.py --size w2048 --phase prefill --batch 8 --prompt 2048 --iters 2
+    python dev/nefelorn_step.py --size w2048 --phase prefill --batch 8 --prompt 2048 --iters 2 [--model salizen]
 """
 import argparse
 import os
@@ -14,6 +14,7 @@ import torch  # noqa: E402
 
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--model", choices=["nefelorn", "salizen"], default="nefelorn")
     ap.add_argument("--size", default="w1024")
     ap.add_argument("--phase", choices=["prefill", "decode"], default="prefill")
     ap.add_argument("--batch", type=int, default=8)
@@ -26,11 +27,14 @@ def main():
     from libai_b200.inference import serving_bench as sb
     from libai_b200.inference.scheduler import RequestScheduler
     from libai_b200.layers._param import param_defaults
-    from libai_b200.models import NefelornForCausalLM
+    from libai_b200.models import NefelornForCausalLM, SalizenForCausalLM
 
     s = sb.NEFELORN_SIZES[a.size]
     with param_defaults(dtype=torch.bfloat16, device="cuda", seed=1):
-        model = NefelornForCausalLM(DictConfig(sb.nefelorn_config(s))).eval().cuda()
+        if a.model == "salizen":
+            model = SalizenForCausalLM(DictConfig(sb.salizen_config(s))).eval().cuda()
+        else:
+            model = NefelornForCausalLM(DictConfig(sb.nefelorn_config(s))).eval().cuda()
     sched = RequestScheduler(model, cuda_graphs=bool(a.graphs))
     ids = torch.randint(1, s["vocab"], (a.batch, a.prompt), generator=torch.Generator().manual_seed(0))
     prompts = [row.tolist() for row in ids]

@@ -450,6 +450,7 @@ decay_scan_kernel(const T* __restrict__ q, long ldq, const T* __restrict__ k, lo
     const int ct = min(CT, n - c0);
     const bool more = c0 + CT < n;
     if (more) fetch(c0 + CT);                   // in flight during the serial walk below
+    asm volatile("" ::: "memory");              // (the loads may not sink below this point, towards their use after the walk)
     const float* buf = sm + cur * buf_floats;
     const float* sk = buf + r * PS; const float* sq = sk + CT * Dp; const float* sg = sq + CT * Dp;
     const float* sv = buf + CT * Dp * (chan ? 3 : 2) + (grp_ok ? grp * NC : 0);
