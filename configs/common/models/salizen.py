@@ -11,8 +11,8 @@ def _moe(ff, experts=8, top=2):
 
 def _parallel(mlp=None):
     left = dict(heads=8, kv_heads=2, dim=64, vdim=64, mask=dict(size=512), scale=0.125, softcap=30.0,
-                rot=dict(dims=32, base=500000.0, scaling=dict(factor=8.0, original=4096, low=1.0, high=4.0)))
-    right = dict(heads=4, dim=64, vdim=128, tau=16.0, decay_rank=16)
+                rot=dict(dims=32, base=1000000.0, scaling=dict(factor=8.0, original=8192, low=1.0, high=4.0)))
+    right = dict(heads=4, dim=64, vdim=128, tau=8.0, decay_rank=16)
     return dict(type="parallel", mixer=dict(left=left, right=right, left_scale=1.0, right_scale=1.0), mlp=mlp)
 
 
@@ -28,7 +28,7 @@ def _lightning(mlp=None):
 cfg = DictConfig(
     dict(
         vocab=32000, width=512, streams=2, norm=dict(eps=1e-6),
-        embedding=dict(scale=22.6, bigram=dict(buckets=65521, mul_prev=31, mul_cur=17)),
+        embedding=dict(scale=22.6, bigram=dict(buckets=65521, mul_prev=31, mul_cur=13)),
         layers=[_parallel(mlp=dict(kind="dense", ff=1408)), _retention(mlp=_moe(512)), _lightning(mlp=dict(kind="dense", ff=1408)),
                 _lightning(mlp=_moe(512))],
         initializer_range=0.02,

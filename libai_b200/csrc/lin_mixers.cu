@@ -111,7 +111,7 @@ __global__ void token_last_kernel(const int64_t* __restrict__ ids, int* __restri
 //   opening the next (h given):     u = sum_s inw[s] x_s;  h = u / sqrt(mean(u^2) + eps) * w
 // mix / out / inw are fp32.  u is kept in shared memory between the two passes over the row.
 // ------------------------------------------------------------------------------------------------------------------
-constexpr int HC_MAXS = 8;
+constexpr int HC_MAXS = 16;
 
 template <typename T, typename Ty>
 __global__ void hc_step_kernel(float* __restrict__ x, long rows, int n, int ns, const Ty* __restrict__ y, long ldy,
@@ -123,7 +123,7 @@ __global__ void hc_step_kernel(float* __restrict__ x, long rows, int n, int ns, 
   __shared__ float coef[HC_MAXS * HC_MAXS + 2 * HC_MAXS];
   __shared__ float red[32];
   const long r = blockIdx.x;
-  if (threadIdx.x < ns * ns) coef[threadIdx.x] = y ? mix[threadIdx.x] : 0.f;
+  for (int i = threadIdx.x; i < ns * ns; i += blockDim.x) coef[i] = y ? mix[i] : 0.f;
   if (threadIdx.x < ns) {
     coef[HC_MAXS * HC_MAXS + threadIdx.x] = y ? outw[threadIdx.x] : 0.f;
     coef[HC_MAXS * HC_MAXS + HC_MAXS + threadIdx.x] = h ? inw[threadIdx.x] : 0.f;
@@ -621,7 +621,9 @@ int lbl_decay_scan(const void* q, long ldq, const void* k, long ldk, const void*
                    const int* slots, const int* past, float* out, int B, int H, int D, int V, int dtype, cudaStream_t s) {
   if (B == 0) return 0;
   if (D > 256 || (!decay && !z) || (z && !zb)) return -1;
-  const int dpt = D <= 64 ? 4 : 8;              // rows per lane: 16 lanes per column group at D = 64 and at D = 128
+  int dpt = D <= 64 ? 4 : 8;                    // rows per lane: 16 lanes per column group at D = 64 and at D = 128
+  // few (sequence, head) pairs: the smaller tile doubles the threads per pair, which hides more of the serial walk's latency
+  if (dpt == 8 && D <= 128 && (long)B * H * ((V + 127) / 128) < 100) dpt = 4;
   int R = 1;
   while (R * dpt < D) R <<= 1;                  // lanes per column group: a power of two <= 32
   const int groups_max = 256 / R;               // column groups of 8 columns in a block of 256 threads

@@ -389,17 +389,17 @@ def salizen_config(s):
     recurrences have as many heads of the same size, dense and expert feed-forwards have Nefelorn's sizes."""
     D, H = s["dim"], s["heads"]
     moe = {"kind": "moe", "expert": {"ff": s["expert_ff"]}, "router": {"experts": s["experts"], "top": s["top"]}}
-    left = {"heads": H, "kv_heads": s["kv_heads"], "dim": D, "vdim": D, "mask": {"size": s["reach"]}, "scale": D ** -0.5, "softcap": 50.0,
-            "rot": {"dims": D // 2, "base": 500000.0, "scaling": {"factor": 4.0, "original": 4096, "low": 1.0, "high": 4.0}}}
-    right = {"heads": H, "dim": D // 2, "vdim": D, "tau": 16.0, "decay_rank": 64}
+    left = {"heads": H, "kv_heads": s["kv_heads"], "dim": D, "vdim": D, "mask": {"size": s["reach"]}, "scale": D ** -0.5, "softcap": 30.0,
+            "rot": {"dims": D // 2, "base": 1000000.0, "scaling": {"factor": 8.0, "original": 8192, "low": 1.0, "high": 4.0}}}
+    right = {"heads": H, "dim": D // 2, "vdim": D, "tau": 8.0, "decay_rank": 64}
     decay = [1.0 - 2.0 ** (-3 - (i % 8)) for i in range(H)]
     kinds = [{"type": "parallel", "mlp": {"kind": "dense", "ff": s["ff"]},
-              "mixer": {"left": left, "right": right, "left_scale": 0.8, "right_scale": 0.5}},
+              "mixer": {"left": left, "right": right, "left_scale": 1.0, "right_scale": 0.7}},
              {"type": "retention", "mlp": moe, "mixer": {"heads": H, "dim": D, "vdim": D, "decay": decay, "rot": {"dims": D, "base": 10000.0}}},
              {"type": "lightning", "mlp": moe, "mixer": {"heads": H, "dim": D, "vdim": D, "decay": decay}},
              {"type": "lightning", "mlp": moe, "mixer": {"heads": H, "dim": D, "vdim": D, "decay": decay}}]
     return dict(vocab=s["vocab"], width=s["width"], streams=2, norm={"eps": 1e-6},
-                embedding={"scale": s["width"] ** 0.5, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}},
+                embedding={"scale": s["width"] ** 0.5, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 13}},
                 layers=[json.loads(json.dumps(kinds[i % 4])) for i in range(s["blocks"])])
 
 
@@ -479,7 +479,7 @@ def kernel_table_salizen(s, batch, prompt):
         ids = torch.randint(0, s["vocab"], (T,), device=dev)
         last = torch.zeros(batch, dtype=torch.int32, device=dev)
         xs = torch.randn(S, T, n, device=dev)
-        add(f"{phase}: token + bigram embedding into {S} streams", _time(lambda: LF.embed_bigram(table, bigram, ids, last, rb, 30.0, 31, 17, 65521, xs), flush=flush),
+        add(f"{phase}: token + bigram embedding into {S} streams", _time(lambda: LF.embed_bigram(table, bigram, ids, last, rb, 30.0, 31, 13, 65521, xs), flush=flush),
             T * n * (4 + 4 * S))
         x1 = torch.randn(T, n, device=dev)
         add(f"{phase}: Nefelorn embedding", _time(lambda: KF.embed_scale(table, ids, 30.0, x1), flush=flush), T * n * 6)
@@ -493,7 +493,7 @@ def kernel_table_salizen(s, batch, prompt):
         # attention side: rotation, cache write, attention with cap + sink + channel gate beside the same kernel without them
         q = torch.randn(T, H * D, device=dev).to(bf)
         kv = torch.randn(T, C, device=dev).to(bf)
-        freq, ms_ = KF.rotary_frequencies(D // 2, 5e5, {"factor": 4.0, "original": 4096, "low": 1.0, "high": 4.0})
+        freq, ms_ = KF.rotary_frequencies(D // 2, 1e6, {"factor": 8.0, "original": 8192, "low": 1.0, "high": 4.0})
         freq = freq.to(dev)
         add(f"{phase}: rotation of queries and keys", _time(lambda: KF.qk_prepare(q, kv[:, :G * D], None, None, freq, ms_, rb, H, G, D, 1e-6, False, False), flush=flush),
             T * (H + G) * D * 4)
@@ -501,7 +501,7 @@ def kernel_table_salizen(s, batch, prompt):
         first = torch.zeros(batch, 0, C, dtype=bf, device=dev)
         wide, narrow = torch.randn(T, H * D, device=dev).to(bf), torch.randn(T, H, device=dev).to(bf)
         yb = torch.empty(T, H * D, dtype=bf, device=dev)
-        extra = dict(softcap=50.0, sink=True, gate_wide=True, out_scale=0.8)
+        extra = dict(softcap=30.0, sink=True, gate_wide=True, out_scale=0.7)
         if phase == "prefill":
             ext = rb.kv_ext([(R, 0, 0)])
             pairs = sum(min(t + 1, R) for t in range(prompt)) * batch
@@ -534,7 +534,7 @@ def kernel_table_salizen(s, batch, prompt):
         z, zb = torch.randn(T, H * Dg, device=dev), torch.randn(H * Dg, device=dev) + 2.0
         Sg = torch.zeros(batch, H, Dg, D, device=dev)
         add(f"{phase}: decay scan, decay logits per key channel (state {Dg} x {D})",
-            _time(lambda: LF.decay_scan(qg, kg, v2, Sg, rb, z=z, zb=zb, tau=16.0, q_scale=Dg ** -0.5), flush=flush),
+            _time(lambda: LF.decay_scan(qg, kg, v2, Sg, rb, z=z, zb=zb, tau=8.0, q_scale=Dg ** -0.5), flush=flush),
             T * H * (Dg * 8 + D * 6) + state_bytes // 2)
         KH = H // 2
         Cq = 2 * KH * D + H * D

@@ -537,7 +537,7 @@ def test_other_sizes(device, tmp_path, case):
         layers = [O.lightning_cfg(heads=1, dim=3, vdim=3, mlp=O.moe_cfg(ff=5, experts=4, top=4)), O.lightning_cfg(mlp=O.moe_cfg(ff=2, experts=1, top=1))]
     elif case == "wide_values":
         layers = [O.lightning_cfg(heads=2, dim=3, vdim=40), O.retention_cfg(heads=1, dim=36, vdim=3, decay=[0.9], rot=O.rot_cfg(6, 20.0)),
-                  O.parallel_cfg(left=O.left_cfg(heads=6, kv_heads=2, dim=4, window=11), right=O.right_cfg(heads=4, dim=3, vdim=5, tau=16.0))]
+                  O.parallel_cfg(left=O.left_cfg(heads=6, kv_heads=2, dim=4, window=11), right=O.right_cfg(heads=4, dim=3, vdim=5, tau=12.0))]
     elif case == "no_rotation":
         layers = [O.retention_cfg(heads=2, dim=6, vdim=4, decay=[0.9, 0.8], rot=O.rot_cfg(0, 1.0)),
                   O.parallel_cfg(left=O.left_cfg(heads=2, kv_heads=1, dim=6, window=5, rot=O.rot_cfg(0, 1.0)))]
