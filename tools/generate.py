@@ -3,7 +3,7 @@
     python tools/generate.py --model DIR --prompts "5 17 3;9 9 12 40" --max-new-tokens 16 [--dtype float32] [--do-sample …]
 
 The model class and loader come from ``config.json`` (``libai_b200.models.utils.model_loader.auto``).  Models with per-sequence
-state (Bumodra, Nefelorn) run through ``RequestScheduler.generate``: one ragged step for all prompts, then one token per live request;
+state (Bumodra, Nefelorn, Salizen) run through ``RequestScheduler.generate``: one ragged step for all prompts, then one token per live request;
 the others through ``Generator.generate`` on a left-padded batch.  Prints one line of generated ids per prompt.
 """
 import argparse
