@@ -683,3 +683,34 @@ def test_serving_precision_and_graphed_steps(tmp_path):
         assert rel_err(e, w) < 1e-1                             # five blocks of width 32 in bf16: the worst position
         assert float(torch.tensor([rel_err(e[i:i + 1], w[i:i + 1]) for i in range(len(w))]).median()) < 3e-2
         assert rel_err(g_, e.float().cpu()) < 1e-6              # a replayed step computes exactly what an eager one does
+
+
+def test_trace_runner_replays_steps(tmp_path):
+    """``bin/trace_run`` on a tiny checkpoint (CPU): a prompt step for two requests, single-token steps, one request ending early;
+    the files it writes hold the wanted logits in the order of the entries."""
+    import subprocess
+    import sys
+
+    import numpy as np
+
+    cfg = mixed_cfg()
+    W = O.random_weights(cfg, seed=8)
+    path = save_model(tmp_path, cfg, W)
+    a, b = tokens(9, seed=4), tokens(6, seed=5)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:7], "want": [0, 6]}, {"id": "b", "tokens": b[:5], "want": [4]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": a[7:8], "want": []}, {"id": "b", "tokens": b[5:6], "want": [0]}], "end": ["b"]},
+             {"step": 2, "entries": [{"id": "a", "tokens": a[8:9], "want": [0]}], "end": ["a"]}]
+    out = os.path.join(str(tmp_path), "out")
+    res = subprocess.run([sys.executable, os.path.join(REPO, "bin", "trace_run"), "--model", path, "--dtype", "float32", "--out", out,
+                          "--max-tokens", "64", "--device", "cpu"], input="\n".join(json.dumps(s) for s in steps) + "\n",
+                         capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stderr[-2000:]
+    assert [ln for ln in res.stdout.split("\n") if ln.startswith("done")] == ["done 0", "done 1", "done 2"]
+    wa, wb = O.forward(cfg, W, a), O.forward(cfg, W, b)
+    vocab = cfg["vocab"]
+    got0 = torch.from_numpy(np.fromfile(os.path.join(out, "0.f32"), dtype="<f4").reshape(-1, vocab).copy())
+    assert rel_err(got0, torch.stack([wa[0], wa[6], wb[4]])) < 1e-4
+    got1 = torch.from_numpy(np.fromfile(os.path.join(out, "1.f32"), dtype="<f4").reshape(-1, vocab).copy())
+    assert rel_err(got1, wb[5:6]) < 1e-4
+    got2 = torch.from_numpy(np.fromfile(os.path.join(out, "2.f32"), dtype="<f4").reshape(-1, vocab).copy())
+    assert rel_err(got2, wa[8:9]) < 1e-4
