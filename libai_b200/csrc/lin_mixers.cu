@@ -109,7 +109,8 @@ __global__ void token_last_kernel(const int64_t* __restrict__ ids, int* __restri
 //                                   the sublayer's output, or - `pos` given - sum_k cw[r,k] * y[pos[r,k]] over sorted
 //                                   expert rows)
 //   opening the next (h given):     u = sum_s inw[s] x_s;  h = u / sqrt(mean(u^2) + eps) * w
-// mix / out / inw are fp32.  u is kept in shared memory between the two passes over the row.
+// mix / out / inw are fp32.  This is the general form (any width and alignment, up to HC_MAXS streams): one channel per thread
+// and access, u kept in shared memory between the two passes over the row.
 // ------------------------------------------------------------------------------------------------------------------
 constexpr int HC_MAXS = 16;
 
@@ -117,7 +118,7 @@ template <typename T, typename Ty>
 __global__ void hc_step_kernel(float* __restrict__ x, long rows, int n, int ns, const Ty* __restrict__ y, long ldy,
                                const int* __restrict__ pos, const float* __restrict__ cw, int top, const float* __restrict__ mix,
                                const float* __restrict__ outw, const float* __restrict__ inw, const T* __restrict__ w, float eps,
-                               T* __restrict__ h, long ldh, int vec) {
+                               T* __restrict__ h, long ldh) {
   extern __shared__ __align__(16) float hc_sm[];
   float* u = hc_sm;                                  // [n] (only with h)
   __shared__ float coef[HC_MAXS * HC_MAXS + 2 * HC_MAXS];
@@ -133,53 +134,7 @@ __global__ void hc_step_kernel(float* __restrict__ x, long rows, int n, int ns, 
   const float* co = coef + HC_MAXS * HC_MAXS;
   const float* ci = co + HC_MAXS;
   float ss = 0.f;
-  if (vec) {
-    for (int c = threadIdx.x * 4; c < n; c += blockDim.x * 4) {
-      float4 xs[HC_MAXS];
-#pragma unroll
-      for (int s = 0; s < HC_MAXS; ++s) if (s < ns) xs[s] = *reinterpret_cast<const float4*>(x + ((long)s * rows + r) * n + c);
-      if (y) {
-        float4 yv;
-        if (pos) {
-          yv = make_float4(0.f, 0.f, 0.f, 0.f);
-          for (int k = 0; k < top; ++k) {
-            const float wk = cw[r * top + k];
-            const float4 t = ld4(y + (long)pos[r * top + k] * ldy + c);
-            yv.x += wk * t.x; yv.y += wk * t.y; yv.z += wk * t.z; yv.w += wk * t.w;
-          }
-        } else {
-          yv = ld4(y + r * ldy + c);
-        }
-        float4 nx[HC_MAXS];
-#pragma unroll
-        for (int t = 0; t < HC_MAXS; ++t) {
-          if (t < ns) {
-            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-            for (int s = 0; s < HC_MAXS; ++s) {
-              if (s < ns) { const float m = cm[s * ns + t]; a.x += m * xs[s].x; a.y += m * xs[s].y; a.z += m * xs[s].z; a.w += m * xs[s].w; }
-            }
-            const float o = co[t];
-            a.x += o * yv.x; a.y += o * yv.y; a.z += o * yv.z; a.w += o * yv.w;
-            nx[t] = a;
-          }
-        }
-#pragma unroll
-        for (int t = 0; t < HC_MAXS; ++t) {
-          if (t < ns) { xs[t] = nx[t]; *reinterpret_cast<float4*>(x + ((long)t * rows + r) * n + c) = nx[t]; }
-        }
-      }
-      if (h) {
-        float4 uv = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int s = 0; s < HC_MAXS; ++s) {
-          if (s < ns) { const float m = ci[s]; uv.x += m * xs[s].x; uv.y += m * xs[s].y; uv.z += m * xs[s].z; uv.w += m * xs[s].w; }
-        }
-        *reinterpret_cast<float4*>(u + c) = uv;
-        ss += uv.x * uv.x + uv.y * uv.y + uv.z * uv.z + uv.w * uv.w;
-      }
-    }
-  } else {
+  {
     for (int c = threadIdx.x; c < n; c += blockDim.x) {
       float xs[HC_MAXS];
 #pragma unroll
@@ -213,14 +168,7 @@ __global__ void hc_step_kernel(float* __restrict__ x, long rows, int n, int ns, 
   if (!h) return;
   ss = block_sum(ss, red);
   const float rr = 1.f / sqrtf(ss / (float)n + eps);
-  if (vec) {
-    for (int c = threadIdx.x * 4; c < n; c += blockDim.x * 4) {
-      const float4 uv = *reinterpret_cast<const float4*>(u + c), wv = ld4(w + c);
-      st4(h + r * ldh + c, make_float4(uv.x * rr * wv.x, uv.y * rr * wv.y, uv.z * rr * wv.z, uv.w * rr * wv.w));
-    }
-  } else {
-    for (int c = threadIdx.x; c < n; c += blockDim.x) stf(h + r * ldh + c, u[c] * rr * ldf(w + c));
-  }
+  for (int c = threadIdx.x; c < n; c += blockDim.x) stf(h + r * ldh + c, u[c] * rr * ldf(w + c));
 }
 
 // The same for rows of 16-byte aligned fp32 quadruples with at most NS streams and ITEMS quadruples per thread: every load of
@@ -522,13 +470,26 @@ decay_scan_kernel(const T* __restrict__ q, long ldq, const T* __restrict__ k, lo
 // ------------------------------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void gated_norm_head_kernel(const float* __restrict__ o, const T* __restrict__ gate, long ldg, const T* __restrict__ w,
-                                       float eps, int act, float out_scale, T* __restrict__ y, long ldy, long rows, int H, int V) {
+                                       float eps, int act, float out_scale, T* __restrict__ y, long ldy, long rows, int H, int V, int vec) {
   const long wid = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (wid >= rows * H) return;
   const long tok = wid / H; const int h = (int)(wid - tok * H);
   const float* orow = o + (tok * H + h) * (long)V;
   float ss = 0.f;
+  if (vec) {                                     // four channels per lane and access (the second pass re-reads o from L1)
+    for (int i = lane * 4; i < V; i += 128) { const float4 a = *reinterpret_cast<const float4*>(orow + i); ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w; }
+    ss = warp_sum(ss);
+    const float rv = out_scale / sqrtf(ss / (float)V + eps);
+    for (int i = lane * 4; i < V; i += 128) {
+      const float4 a = *reinterpret_cast<const float4*>(orow + i), g = ld4(gate + tok * ldg + h * V + i);
+      const float4 wv = w ? ld4(w + i) : make_float4(1.f, 1.f, 1.f, 1.f);
+      const float4 ga = act == 0 ? make_float4(siluf_(g.x), siluf_(g.y), siluf_(g.z), siluf_(g.w))
+                                 : make_float4(sigmoidf_(g.x), sigmoidf_(g.y), sigmoidf_(g.z), sigmoidf_(g.w));
+      st4(y + tok * ldy + h * V + i, make_float4(a.x * rv * wv.x * ga.x, a.y * rv * wv.y * ga.y, a.z * rv * wv.z * ga.z, a.w * rv * wv.w * ga.w));
+    }
+    return;
+  }
   for (int i = lane; i < V; i += 32) ss += orow[i] * orow[i];
   ss = warp_sum(ss);
   const float rr = out_scale / sqrtf(ss / (float)V + eps);
@@ -541,11 +502,24 @@ __global__ void gated_norm_head_kernel(const float* __restrict__ o, const T* __r
 
 template <typename T>
 __global__ void gated_norm_row_kernel(const float* __restrict__ o, const T* __restrict__ gate, long ldg, const T* __restrict__ w,
-                                      float eps, int act, float out_scale, T* __restrict__ y, long ldy, int n) {
+                                      float eps, int act, float out_scale, T* __restrict__ y, long ldy, int n, int vec) {
   __shared__ float red[32];
   const long tok = blockIdx.x;
   const float* orow = o + tok * (long)n;
   float ss = 0.f;
+  if (vec) {
+    for (int i = threadIdx.x * 4; i < n; i += blockDim.x * 4) { const float4 a = *reinterpret_cast<const float4*>(orow + i); ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w; }
+    ss = block_sum(ss, red);
+    const float rv = out_scale / sqrtf(ss / (float)n + eps);
+    for (int i = threadIdx.x * 4; i < n; i += blockDim.x * 4) {
+      const float4 a = *reinterpret_cast<const float4*>(orow + i), g = ld4(gate + tok * ldg + i);
+      const float4 wv = w ? ld4(w + i) : make_float4(1.f, 1.f, 1.f, 1.f);
+      const float4 ga = act == 0 ? make_float4(siluf_(g.x), siluf_(g.y), siluf_(g.z), siluf_(g.w))
+                                 : make_float4(sigmoidf_(g.x), sigmoidf_(g.y), sigmoidf_(g.z), sigmoidf_(g.w));
+      st4(y + tok * ldy + i, make_float4(a.x * rv * wv.x * ga.x, a.y * rv * wv.y * ga.y, a.z * rv * wv.z * ga.z, a.w * rv * wv.w * ga.w));
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < n; i += blockDim.x) ss += orow[i] * orow[i];
   ss = block_sum(ss, red);
   const float rr = out_scale / sqrtf(ss / (float)n + eps);
@@ -609,7 +583,7 @@ int lbl_hc_step(float* x, long rows, int n, int ns, const void* y, long ldy, int
 #define HC(TT, TY) { \
     if (smem > 48 * 1024) cudaFuncSetAttribute(hc_step_kernel<TT, TY>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     hc_step_kernel<TT, TY><<<(unsigned)rows, threads, smem, s>>>(x, rows, n, ns, (const TY*)y, ldy, pos, cw, top, mix, outw, inw, \
-                                                                 (const TT*)w, eps, (TT*)h, ldh, vec); }
+                                                                 (const TT*)w, eps, (TT*)h, ldh); }
   if (dtype) { if (ydtype) HC(bf16, bf16) else HC(bf16, float) }
   else { if (ydtype) return -1; HC(float, float) }
 #undef HC
@@ -655,14 +629,16 @@ int lbl_decay_scan(const void* q, long ldq, const void* k, long ldk, const void*
 int lbl_gated_norm(const float* o, const void* gate, long ldg, const void* w, float eps, int act, float out_scale, void* y, long ldy,
                    long rows, int H, int V, int per_head, int dtype, cudaStream_t s) {
   if (rows == 0) return 0;
+  const int vec = (V % 4 == 0 && ldg % 4 == 0 && ldy % 4 == 0 && ((uintptr_t)o & 15) == 0 && ((uintptr_t)gate & 15) == 0 &&
+                   ((uintptr_t)y & 15) == 0 && ((uintptr_t)w & 15) == 0) ? 1 : 0;
   if (per_head) {
     const unsigned grid = (unsigned)((rows * H * 32 + 255) / 256);
-    if (dtype) gated_norm_head_kernel<bf16><<<grid, 256, 0, s>>>(o, (const bf16*)gate, ldg, (const bf16*)w, eps, act, out_scale, (bf16*)y, ldy, rows, H, V);
-    else gated_norm_head_kernel<float><<<grid, 256, 0, s>>>(o, (const float*)gate, ldg, (const float*)w, eps, act, out_scale, (float*)y, ldy, rows, H, V);
+    if (dtype) gated_norm_head_kernel<bf16><<<grid, 256, 0, s>>>(o, (const bf16*)gate, ldg, (const bf16*)w, eps, act, out_scale, (bf16*)y, ldy, rows, H, V, vec);
+    else gated_norm_head_kernel<float><<<grid, 256, 0, s>>>(o, (const float*)gate, ldg, (const float*)w, eps, act, out_scale, (float*)y, ldy, rows, H, V, vec);
   } else {
     const int n = H * V, threads = n >= 1024 ? 256 : 128;
-    if (dtype) gated_norm_row_kernel<bf16><<<(unsigned)rows, threads, 0, s>>>(o, (const bf16*)gate, ldg, (const bf16*)w, eps, act, out_scale, (bf16*)y, ldy, n);
-    else gated_norm_row_kernel<float><<<(unsigned)rows, threads, 0, s>>>(o, (const float*)gate, ldg, (const float*)w, eps, act, out_scale, (float*)y, ldy, n);
+    if (dtype) gated_norm_row_kernel<bf16><<<(unsigned)rows, threads, 0, s>>>(o, (const bf16*)gate, ldg, (const bf16*)w, eps, act, out_scale, (bf16*)y, ldy, n, vec);
+    else gated_norm_row_kernel<float><<<(unsigned)rows, threads, 0, s>>>(o, (const float*)gate, ldg, (const float*)w, eps, act, out_scale, (float*)y, ldy, n, vec);
   }
   LAUNCH_END();
 }
