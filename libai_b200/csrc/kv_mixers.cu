@@ -196,20 +196,30 @@ __device__ __forceinline__ float act_apply(float v, int act) {
     default: return v;
   }
 }
+// gated pair (g, u) -> act(g) * u; act 5 is the clamped form  g' = min(g, limit), u' = clamp(u, -limit, limit),
+// g' * sigmoid(1.702 g') * (u' + 1)
+__device__ __forceinline__ float gated_apply(float g, float u, int act, float limit) {
+  if (act == 5) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g * sigmoidf_(1.702f * g) * (u + 1.f);
+  }
+  return act_apply(g, act) * u;
+}
 template <typename T>
-__global__ void act_rows_kernel(const T* in, long ldi, T* out, long ldo, long rows, int n, int act, int gated) {   // in == out is allowed
+__global__ void act_rows_kernel(const T* in, long ldi, T* out, long ldo, long rows, int n, int act, int gated, float limit) {   // in == out is allowed
   const long total = rows * n;
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
     const long r = i / n; const int c = (int)(i - r * n);
-    float v = act_apply(ldf(in + r * ldi + c), act);
-    if (gated) v *= ldf(in + r * ldi + n + c);
+    float v = ldf(in + r * ldi + c);
+    v = gated ? gated_apply(v, ldf(in + r * ldi + n + c), act, limit) : act_apply(v, act);
     stf(out + r * ldo + c, v);
   }
 }
 
 // bf16, 8 channels per thread with 16-byte accesses (n a multiple of 8, rows 16-byte aligned)
 __global__ void act_rows_vec8_kernel(const __nv_bfloat16* in, long ldi, __nv_bfloat16* out, long ldo, long rows, int n, int act,
-                                     int gated) {
+                                     int gated, float limit) {
   const int per = n / 8;
   const long total = rows * per;
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
@@ -224,8 +234,8 @@ __global__ void act_rows_vec8_kernel(const __nv_bfloat16* in, long ldi, __nv_bfl
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       float2 v = __bfloat1622float2(a2[j]);
-      v.x = act_apply(v.x, act); v.y = act_apply(v.y, act);
-      if (gated) { const float2 u = __bfloat1622float2(b2[j]); v.x *= u.x; v.y *= u.y; }
+      if (gated) { const float2 u = __bfloat1622float2(b2[j]); v.x = gated_apply(v.x, u.x, act, limit); v.y = gated_apply(v.y, u.y, act, limit); }
+      else { v.x = act_apply(v.x, act); v.y = act_apply(v.y, act); }
       o2[j] = __floats2bfloat162_rn(v.x, v.y);
     }
     *reinterpret_cast<uint4*>(out + r * ldo + c) = o;
@@ -871,15 +881,18 @@ __global__ void ring_decode_merge_kernel(const float* __restrict__ part, const T
 // ------------------------------------------------------------------------------------------------------------------
 // Mixture of experts.
 //   moe_topk    : from the fp32 router logits z = W_r h (a product of the caller's): s = sigmoid(z), the `top` largest
-//                 (ties: the lower index), weights s / (sum + 1e-20) * rscale; optionally counts the tokens of every expert.
+//                 (ties: the lower index), weights s / (sum + 1e-20) * rscale (mode 2: the scores themselves, s * rscale);
+//                 optionally counts the tokens of every expert.
 //   pair kernels: few tokens (single-token steps): every (token, chosen expert) pair reads its expert's matrices —
-//                 a = act(W_gate h) * (W_up h), then out[t] = sum_k weight_k W_down,k a_k in fp32.
+//                 a = act(W_gate h) * (W_up h), then out[t] = sum_k weight_k W_down,k a_k in fp32.  `win` puts the weight on
+//                 the expert's input instead: the pair reads weight_k * h (rounded to T) and the outputs are summed.
 //   sort kernels: many tokens: rows are copied into a matrix sorted by expert (offsets from the counts), the experts
 //                 run as dense products on their row ranges, and the fused residual kernel gathers the weighted sum.
 // Expert matrices are stacked: wgu [E, 2*ff, n] (gate rows, then up rows), wd [E, n, ff].
 // ------------------------------------------------------------------------------------------------------------------
 // one warp per token over its fp32 router logits z [tokens, E] (+ bias [E] when given).  mode 0: scores sigmoid(z), weights
-// score / (sum of the chosen scores + 1e-20) * rscale; mode 1: scores z, weights = softmax over the chosen logits, times rscale
+// score / (sum of the chosen scores + 1e-20) * rscale; mode 1: scores z, weights = softmax over the chosen logits, times rscale;
+// mode 2: scores sigmoid(z), weights = the chosen scores as they are, times rscale
 __global__ void moe_topk_kernel(const float* __restrict__ z, long ldz, const float* __restrict__ bias, int mode, int E, int top,
                                 float rscale, int* __restrict__ idx, float* __restrict__ wts, int* __restrict__ counts, long tokens) {
   extern __shared__ float sm[];
@@ -889,7 +902,7 @@ __global__ void moe_topk_kernel(const float* __restrict__ z, long ldz, const flo
   if (tok >= tokens) return;                     // warps are independent below
   for (int e = lane; e < E; e += 32) {
     const float v = z[tok * ldz + e] + (bias ? bias[e] : 0.f);
-    sc[e] = mode == 0 ? sigmoidf_(v) : v;
+    sc[e] = mode == 1 ? v : sigmoidf_(v);
   }
   __syncwarp();
   float sum = 0.f, mine_w = 0.f, first = 0.f; int mine_e = 0;
@@ -903,7 +916,7 @@ __global__ void moe_topk_kernel(const float* __restrict__ z, long ldz, const flo
       if (ov > best || (ov == best && oe < be)) { best = ov; be = oe; }
     }
     if (k == 0) first = best;
-    const float wk = mode == 0 ? best : expf(best - first);   // the first choice is the largest logit
+    const float wk = mode != 1 ? best : expf(best - first);   // the first choice is the largest logit
     sum += wk;
     if (lane == k % 32) { mine_w = wk; mine_e = be; }
     if (lane == 0) sc[be] = -INFINITY;
@@ -914,7 +927,7 @@ __global__ void moe_topk_kernel(const float* __restrict__ z, long ldz, const flo
     }
   }
   __syncwarp();
-  const float inv = rscale / (mode == 0 ? sum + 1e-20f : sum);
+  const float inv = mode == 2 ? rscale : rscale / (mode == 0 ? sum + 1e-20f : sum);
   for (int k = lane; k < top; k += 32) {
     wts[tok * top + k] *= inv;
     if (counts) atomicAdd(counts + idx[tok * top + k], 1);
@@ -923,13 +936,18 @@ __global__ void moe_topk_kernel(const float* __restrict__ z, long ldz, const flo
 
 template <typename T>
 __global__ void __launch_bounds__(256)
-moe_pair_gateup_kernel(const T* __restrict__ h, long ldh, const T* __restrict__ wgu, const int* __restrict__ idx, T* __restrict__ a,
-                       int ff, int n, int top, int act) {
+moe_pair_gateup_kernel(const T* __restrict__ h, long ldh, const T* __restrict__ wgu, const int* __restrict__ idx,
+                       const float* __restrict__ wts, int win, T* __restrict__ a, int ff, int n, int top, int act, float limit) {
   extern __shared__ float sm[];
   const long pair = blockIdx.x;
   const long tok = pair / top;
   const int e = idx[pair];
-  for (int i = threadIdx.x; i < n; i += blockDim.x) sm[i] = ldf(h + tok * ldh + i);
+  if (win) {
+    const float wp = wts[pair];
+    for (int i = threadIdx.x; i < n; i += blockDim.x) { T r; stf(&r, wp * ldf(h + tok * ldh + i)); sm[i] = ldf(&r); }
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) sm[i] = ldf(h + tok * ldh + i);
+  }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const int per = (ff + gridDim.y - 1) / gridDim.y;
@@ -938,14 +956,14 @@ moe_pair_gateup_kernel(const T* __restrict__ h, long ldh, const T* __restrict__ 
   for (int f = f0 + warp; f < f1; f += nw) {
     const float gv = warp_dot<T>(wg + (long)f * n, sm, n, lane);
     const float uv = warp_dot<T>(wg + (long)(ff + f) * n, sm, n, lane);
-    if (lane == 0) stf(a + pair * ff + f, act_apply(gv, act) * uv);
+    if (lane == 0) stf(a + pair * ff + f, gated_apply(gv, uv, act, limit));
   }
 }
 
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_pair_down_kernel(const T* __restrict__ a, const T* __restrict__ wd, const int* __restrict__ idx, const float* __restrict__ wts,
-                     float* __restrict__ out, int ff, int n, int top) {
+                     int win, float* __restrict__ out, int ff, int n, int top) {
   extern __shared__ float sm[];
   const long tok = blockIdx.x;
   for (int i = threadIdx.x; i < top * ff; i += blockDim.x) sm[i] = ldf(a + tok * top * ff + i);
@@ -957,7 +975,7 @@ moe_pair_down_kernel(const T* __restrict__ a, const T* __restrict__ wd, const in
     float acc = 0.f;
     for (int k = 0; k < top; ++k) {
       const int e = idx[tok * top + k];
-      acc += wts[tok * top + k] * warp_dot<T>(wd + ((long)e * n + c) * ff, sm + k * ff, ff, lane);
+      acc += (win ? 1.f : wts[tok * top + k]) * warp_dot<T>(wd + ((long)e * n + c) * ff, sm + k * ff, ff, lane);
     }
     if (lane == 0) out[tok * n + c] = acc;
   }
@@ -990,7 +1008,8 @@ __global__ void moe_offsets_kernel(const int* __restrict__ counts, int* __restri
 
 template <typename T>
 __global__ void moe_scatter_kernel(const T* __restrict__ h, long ldh, const int* __restrict__ idx, const int* __restrict__ offsets,
-                                   int* __restrict__ cursor, int* __restrict__ pos, T* __restrict__ xs, int n, int top) {
+                                   int* __restrict__ cursor, int* __restrict__ pos, T* __restrict__ xs, int n, int top,
+                                   const float* __restrict__ wts) {   // wts given: the copied row is wts[pair] * h
   __shared__ int where;
   const long pair = blockIdx.x;
   if (threadIdx.x == 0) {
@@ -1002,7 +1021,10 @@ __global__ void moe_scatter_kernel(const T* __restrict__ h, long ldh, const int*
   const T* src = h + (pair / top) * ldh;
   T* dst = xs + (long)where * n;
   constexpr int PER = 16 / sizeof(T);
-  if (n % PER == 0 && ldh % PER == 0 && ((uintptr_t)h & 15) == 0 && ((uintptr_t)xs & 15) == 0) {
+  if (wts) {
+    const float wp = wts[pair];
+    for (int i = threadIdx.x; i < n; i += blockDim.x) stf(dst + i, wp * ldf(src + i));
+  } else if (n % PER == 0 && ldh % PER == 0 && ((uintptr_t)h & 15) == 0 && ((uintptr_t)xs & 15) == 0) {
     for (int i = threadIdx.x; i < n / PER; i += blockDim.x)
       reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
   } else {
@@ -1052,18 +1074,20 @@ int lbk_dyt_residual(float* x, const void* y, long ldy, int ydtype, const int* p
   LAUNCH_END();
 }
 
-int lbk_act_rows(const void* in, long ldi, void* out, long ldo, long rows, int n, int act, int gated, int dtype, cudaStream_t s) {
+int lbk_act_rows(const void* in, long ldi, void* out, long ldo, long rows, int n, int act, int gated, float limit, int dtype,
+                 cudaStream_t s) {
+  if (act == 5 && !gated) return -1;
   if (rows == 0 || n == 0) return 0;
   const long total = rows * n;
   if (dtype && n % 8 == 0 && ldi % 8 == 0 && ldo % 8 == 0 && ((uintptr_t)in & 15) == 0 && ((uintptr_t)out & 15) == 0) {
     const long work = total / 8;
     const unsigned g8 = (unsigned)((work + 255) / 256 > 148 * 16 ? 148 * 16 : (work + 255) / 256);
-    act_rows_vec8_kernel<<<g8, 256, 0, s>>>((const bf16*)in, ldi, (bf16*)out, ldo, rows, n, act, gated);
+    act_rows_vec8_kernel<<<g8, 256, 0, s>>>((const bf16*)in, ldi, (bf16*)out, ldo, rows, n, act, gated, limit);
     LAUNCH_END();
   }
   const unsigned grid = (unsigned)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
-  if (dtype) act_rows_kernel<bf16><<<grid, 256, 0, s>>>((const bf16*)in, ldi, (bf16*)out, ldo, rows, n, act, gated);
-  else act_rows_kernel<float><<<grid, 256, 0, s>>>((const float*)in, ldi, (float*)out, ldo, rows, n, act, gated);
+  if (dtype) act_rows_kernel<bf16><<<grid, 256, 0, s>>>((const bf16*)in, ldi, (bf16*)out, ldo, rows, n, act, gated, limit);
+  else act_rows_kernel<float><<<grid, 256, 0, s>>>((const float*)in, ldi, (float*)out, ldo, rows, n, act, gated, limit);
   LAUNCH_END();
 }
 
@@ -1139,7 +1163,7 @@ int lbk_moe_topk(const float* z, long ldz, const float* bias, int mode, int E, i
 }
 
 int lbk_moe_pairs(const void* h, long ldh, const void* wgu, const void* wd, const int* idx, const float* wts, void* a, float* out,
-                  long tokens, int ff, int n, int top, int act, int dtype, cudaStream_t s) {
+                  long tokens, int ff, int n, int top, int act, float limit, int win, int dtype, cudaStream_t s) {
   if (tokens == 0) return 0;
   const size_t smem1 = (size_t)n * sizeof(float), smem2 = (size_t)top * ff * sizeof(float);
   if (smem1 > 200 * 1024 || smem2 > 200 * 1024) return -1;
@@ -1150,25 +1174,25 @@ int lbk_moe_pairs(const void* h, long ldh, const void* wgu, const void* wd, cons
   if (dtype) {
     if (smem1 > 48 * 1024) cudaFuncSetAttribute(moe_pair_gateup_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
     if (smem2 > 48 * 1024) cudaFuncSetAttribute(moe_pair_down_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
-    moe_pair_gateup_kernel<bf16><<<dim3((unsigned)pairs, sy1), 256, smem1, s>>>((const bf16*)h, ldh, (const bf16*)wgu, idx, (bf16*)a, ff, n, top, act);
-    moe_pair_down_kernel<bf16><<<dim3((unsigned)tokens, sy2), 256, smem2, s>>>((const bf16*)a, (const bf16*)wd, idx, wts, out, ff, n, top);
+    moe_pair_gateup_kernel<bf16><<<dim3((unsigned)pairs, sy1), 256, smem1, s>>>((const bf16*)h, ldh, (const bf16*)wgu, idx, wts, win, (bf16*)a, ff, n, top, act, limit);
+    moe_pair_down_kernel<bf16><<<dim3((unsigned)tokens, sy2), 256, smem2, s>>>((const bf16*)a, (const bf16*)wd, idx, wts, win, out, ff, n, top);
   } else {
     if (smem1 > 48 * 1024) cudaFuncSetAttribute(moe_pair_gateup_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
     if (smem2 > 48 * 1024) cudaFuncSetAttribute(moe_pair_down_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
-    moe_pair_gateup_kernel<float><<<dim3((unsigned)pairs, sy1), 256, smem1, s>>>((const float*)h, ldh, (const float*)wgu, idx, (float*)a, ff, n, top, act);
-    moe_pair_down_kernel<float><<<dim3((unsigned)tokens, sy2), 256, smem2, s>>>((const float*)a, (const float*)wd, idx, wts, out, ff, n, top);
+    moe_pair_gateup_kernel<float><<<dim3((unsigned)pairs, sy1), 256, smem1, s>>>((const float*)h, ldh, (const float*)wgu, idx, wts, win, (float*)a, ff, n, top, act, limit);
+    moe_pair_down_kernel<float><<<dim3((unsigned)tokens, sy2), 256, smem2, s>>>((const float*)a, (const float*)wd, idx, wts, win, out, ff, n, top);
   }
   LAUNCH_END();
 }
 
 int lbk_moe_sort(const void* h, long ldh, const int* idx, const int* counts, int* offsets, int* cursor, int* pos, void* xs, long tokens,
-                 int E, int n, int top, int align, int* tile_group, int tiles, int dtype, cudaStream_t s) {
+                 int E, int n, int top, int align, int* tile_group, int tiles, const float* wts, int dtype, cudaStream_t s) {
   if (tokens == 0) return 0;
   if (E > 1024 || align < 1) return -1;
   moe_offsets_kernel<<<1, 256, 0, s>>>(counts, offsets, cursor, E, align, tile_group, tiles);
   const unsigned pairs = (unsigned)(tokens * top);
-  if (dtype) moe_scatter_kernel<bf16><<<pairs, 128, 0, s>>>((const bf16*)h, ldh, idx, offsets, cursor, pos, (bf16*)xs, n, top);
-  else moe_scatter_kernel<float><<<pairs, 128, 0, s>>>((const float*)h, ldh, idx, offsets, cursor, pos, (float*)xs, n, top);
+  if (dtype) moe_scatter_kernel<bf16><<<pairs, 128, 0, s>>>((const bf16*)h, ldh, idx, offsets, cursor, pos, (bf16*)xs, n, top, wts);
+  else moe_scatter_kernel<float><<<pairs, 128, 0, s>>>((const float*)h, ldh, idx, offsets, cursor, pos, (float*)xs, n, top, wts);
   LAUNCH_END();
 }
 

@@ -14,8 +14,9 @@ int lbl_hc_step(float* x, long rows, int n, int ns, const void* y, long ldy, int
                 const float* mix, const float* outw, const float* inw, const void* w, float eps, void* h, long ldh, int dtype,
                 cudaStream_t s);
 int lbl_decay_scan(const void* q, long ldq, const void* k, long ldk, const void* v, long ldv, const float* decay, const float* z,
-                   long ldz, const float* zb, float inv_tau, float q_scale, float k_scale, int act, float* S, const int* seq_off,
-                   const int* slots, const int* past, float* out, int B, int H, int D, int V, int dtype, cudaStream_t s);
+                   long ldz, const float* zb, const float* lower, float inv_tau, float q_scale, float k_scale, int act, float* S,
+                   const int* seq_off, const int* slots, const int* past, float* out, int B, int H, int D, int V, int dtype,
+                   cudaStream_t s);
 int lbl_gated_norm(const float* o, const void* gate, long ldg, const void* w, float eps, int act, float out_scale, void* y, long ldy,
                    long rows, int H, int V, int per_head, int dtype, cudaStream_t s);
 }
@@ -94,7 +95,8 @@ void hc_step(Tensor x, const OptT& y, const OptT& pos, const OptT& cw, const Opt
 }
 
 void decay_scan(const Tensor& q, const Tensor& k, const Tensor& v, const OptT& decay, const OptT& z, const OptT& zb, double inv_tau,
-                double q_scale, double k_scale, bool act, Tensor S, const Tensor& seq_off, const Tensor& slots, const Tensor& past, Tensor out) {
+                double q_scale, double k_scale, int64_t act, Tensor S, const Tensor& seq_off, const Tensor& slots, const Tensor& past, Tensor out,
+                const OptT& lower) {
   rows2d(q, "decay_scan q"); rows2d(k, "decay_scan k"); rows2d(v, "decay_scan v");
   TORCH_CHECK(S.is_cuda() && S.dim() == 4 && S.is_contiguous() && S.scalar_type() == at::kFloat, "decay_scan: S must be fp32 [slots, H, D, V]");
   const int H = (int)S.size(1), D = (int)S.size(2), V = (int)S.size(3);
@@ -102,7 +104,8 @@ void decay_scan(const Tensor& q, const Tensor& k, const Tensor& v, const OptT& d
               code(q) == code(k) && code(q) == code(v), "decay_scan: q, k [tokens, H*D], v [tokens, H*V] of one dtype");
   TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kFloat && out.is_contiguous() && out.dim() == 2 && out.size(1) == (long)H * V &&
               out.size(0) == q.size(0), "decay_scan: out must be fp32 [tokens, H*V]");
-  const float* dp = nullptr; const float* zp = nullptr; const float* bp = nullptr; long ldz = 0;
+  const float* dp = nullptr; const float* zp = nullptr; const float* bp = nullptr; const float* lp = nullptr; long ldz = 0;
+  if (has(lower)) { TORCH_CHECK(has(z), "decay_scan: a lower bound needs decay logits"); lp = f32(*lower, (int64_t)H * D, "decay_scan lower"); }
   if (has(z)) {
     rows2d(*z, "decay_scan z");
     TORCH_CHECK(z->scalar_type() == at::kFloat && z->size(0) == q.size(0) && z->size(1) == (long)H * D && has(zb), "decay_scan: z fp32 [tokens, H*D] with its bias");
@@ -112,13 +115,15 @@ void decay_scan(const Tensor& q, const Tensor& k, const Tensor& v, const OptT& d
     dp = f32(*decay, H, "decay_scan decay");
   }
   c10::cuda::CUDAGuard guard(q.device());
-  check(lbl_decay_scan(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), dp, zp, ldz, bp, (float)inv_tau,
-                       (float)q_scale, (float)k_scale, act ? 1 : 0, S.data_ptr<float>(), meta(seq_off), meta(slots), meta(past),
+  check(lbl_decay_scan(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), dp, zp, ldz, bp, lp, (float)inv_tau,
+                       (float)q_scale, (float)k_scale, (int)act, S.data_ptr<float>(), meta(seq_off), meta(slots), meta(past),
                        out.data_ptr<float>(), (int)slots.numel(), H, D, V, code(q), cur_stream()), "decay_scan");
 }
 
-void gated_norm(const Tensor& o, const Tensor& gate, const OptT& w, double eps, int64_t act, double out_scale, Tensor y, int64_t H, int64_t V,
+void gated_norm(const Tensor& o, const OptT& gate_opt, const OptT& w, double eps, int64_t act, double out_scale, Tensor y, int64_t H, int64_t V,
                 bool per_head) {
+  TORCH_CHECK(has(gate_opt) || act == 2, "gated_norm: a gate, or act 2 (none)");
+  const Tensor& gate = has(gate_opt) ? *gate_opt : y;      // act 2 reads no gate
   rows2d(gate, "gated_norm gate"); rows2d(y, "gated_norm y");
   TORCH_CHECK(o.is_cuda() && o.scalar_type() == at::kFloat && o.is_contiguous() && o.numel() == y.size(0) * H * V, "gated_norm: o fp32 [rows, H*V]");
   TORCH_CHECK(gate.size(1) == H * V && gate.size(0) == y.size(0) && y.size(1) == H * V && code(gate) == code(y), "gated_norm: shapes");
@@ -136,6 +141,6 @@ void gated_norm(const Tensor& o, const Tensor& gate, const OptT& w, double eps, 
 TORCH_LIBRARY(libai_b200_lin, m) {
   m.def("embed_bigram(Tensor table, Tensor bigram, Tensor ids, Tensor(a!) last, Tensor tok_seq, Tensor seq_off, Tensor slots, Tensor past, float scale, int mul_prev, int mul_cur, int buckets, Tensor(b!) x) -> ()", &embed_bigram);
   m.def("hc_step(Tensor(a!) x, Tensor? y, Tensor? pos, Tensor? cw, Tensor? mix, Tensor? outw, Tensor? inw, Tensor? w, float eps, Tensor(b!)? h) -> ()", &hc_step);
-  m.def("decay_scan(Tensor q, Tensor k, Tensor v, Tensor? decay, Tensor? z, Tensor? zb, float inv_tau, float q_scale, float k_scale, bool act, Tensor(a!) S, Tensor seq_off, Tensor slots, Tensor past, Tensor(b!) out) -> ()", &decay_scan);
-  m.def("gated_norm(Tensor o, Tensor gate, Tensor? w, float eps, int act, float out_scale, Tensor(a!) y, int H, int V, bool per_head) -> ()", &gated_norm);
+  m.def("decay_scan(Tensor q, Tensor k, Tensor v, Tensor? decay, Tensor? z, Tensor? zb, float inv_tau, float q_scale, float k_scale, int act, Tensor(a!) S, Tensor seq_off, Tensor slots, Tensor past, Tensor(b!) out, Tensor? lower=None) -> ()", &decay_scan);
+  m.def("gated_norm(Tensor o, Tensor? gate, Tensor? w, float eps, int act, float out_scale, Tensor(a!) y, int H, int V, bool per_head) -> ()", &gated_norm);
 }

@@ -257,8 +257,10 @@ __global__ void hc_step_vec_kernel(float* __restrict__ x, long rows, int n, int 
 //   S <- diag(a_t) S + k_t v_t^T;   o_t = S^T q_t
 // a_t is one fixed number per head (`decay` [H], `z` absent) or one per key channel and token,
 // a = sigmoid(z + zb)^(inv_tau) = exp(inv_tau * log sigmoid(z + zb)) with the logits z [tokens, H*D] in fp32.
-// q, k, v are column slices of the projection output (row stride ld*); `act` 1 passes them through SiLU; q is
-// multiplied by q_scale and k by k_scale (fp32).
+// With `lower` [H*D] the decay is bounded from below and also decides what is written (the forget gate of HGRN2):
+//   a = lower + (1 - lower) * sigmoid(z + zb),   k = 1 - a   (the k argument is not read).
+// q, k, v are column slices of the projection output (row stride ld*); `act` is a bit mask of the ones that pass through
+// SiLU (1: q, 2: k, 4: v); q is multiplied by q_scale and k by k_scale (fp32).
 //
 // Columns of S are independent: a block owns `VT` of them for one (sequence, head).  A thread keeps a DPT x 8 tile of S
 // in registers: DPT consecutive key rows (lane r of the R = ceil(D/DPT) adjacent lanes that share a column group) of 8
@@ -295,8 +297,8 @@ template <> __device__ __forceinline__ void ldn<bf16, 8>(const bf16* p, float (&
 template <typename T, int DPT>
 __global__ void __launch_bounds__(256, 1)
 decay_scan_kernel(const T* __restrict__ q, long ldq, const T* __restrict__ k, long ldk, const T* __restrict__ v, long ldv,
-                  const float* __restrict__ decay, const float* __restrict__ z, long ldz, const float* __restrict__ zb, float inv_tau,
-                  float q_scale, float k_scale, int act, float* __restrict__ S, const int* __restrict__ seq_off,
+                  const float* __restrict__ decay, const float* __restrict__ z, long ldz, const float* __restrict__ zb,
+                  const float* __restrict__ lower, float inv_tau, float q_scale, float k_scale, int act, float* __restrict__ S, const int* __restrict__ seq_off,
                   const int* __restrict__ slots, const int* __restrict__ past, float* __restrict__ out, int H, int D, int V, int R,
                   int VT, int CT, int vec) {
   extern __shared__ __align__(16) float sm[];
@@ -324,7 +326,7 @@ decay_scan_kernel(const T* __restrict__ q, long ldq, const T* __restrict__ k, lo
   // staging work of this thread: one (token, lane chunk) of q / k / decays and one (token, column group) of v per group of CT
   // tokens (the launcher picks CT so that both fit the block)
   const int qk_items = CT * R, v_items = CT * (VT / NC);
-  float rk[DPT], rq[DPT], rg[DPT], rv[NC];
+  float rk[DPT], rq[DPT], rg[DPT], rl[DPT], rv[NC];
   auto fetch = [&](int c0) {                    // global loads of the group that starts at token c0, into registers
     const int ct = min(CT, n - c0);
     if (tid < qk_items) {
@@ -332,7 +334,8 @@ decay_scan_kernel(const T* __restrict__ q, long ldq, const T* __restrict__ k, lo
       const long row = tok0 + c0 + t;
       const int i0 = rr * DPT;
       if (t < ct && vec && i0 + DPT <= D) {
-        ldn<T, DPT>(k + row * ldk + h * D + i0, rk);
+        if (!lower) ldn<T, DPT>(k + row * ldk + h * D + i0, rk);
+        else ldn<float, DPT>(lower + h * D + i0, rl);
         ldn<T, DPT>(q + row * ldq + h * D + i0, rq);
         if (chan) {
           ldn<float, DPT>(z + row * ldz + h * D + i0, rg);
@@ -345,7 +348,8 @@ decay_scan_kernel(const T* __restrict__ q, long ldq, const T* __restrict__ k, lo
 #pragma unroll
         for (int d = 0; d < DPT; ++d) {
           const bool in = t < ct && i0 + d < D;
-          rk[d] = in ? ldf(k + row * ldk + h * D + i0 + d) : 0.f;
+          rk[d] = (in && !lower) ? ldf(k + row * ldk + h * D + i0 + d) : 0.f;
+          if (lower) rl[d] = in ? lower[h * D + i0 + d] : 1.f;                              // a = 1, k = 0: the state stays
           rq[d] = in ? ldf(q + row * ldq + h * D + i0 + d) : 0.f;
           if (chan) rg[d] = in ? z[row * ldz + h * D + i0 + d] + zb[h * D + i0 + d] : 1e30f;   // sigmoid(huge) = 1: no decay
         }
@@ -371,9 +375,14 @@ decay_scan_kernel(const T* __restrict__ q, long ldq, const T* __restrict__ k, lo
 #pragma unroll
       for (int d = 0; d < DPT; ++d) {
         float kv = rk[d], qv = rq[d];
-        if (act) { kv = siluf_(kv); qv = siluf_(qv); }
-        ko[d] = kv * k_scale; qo[d] = qv * q_scale;
+        if (act & 1) qv = siluf_(qv);
+        if (act & 2) kv = siluf_(kv);
         go[d] = chan ? expf(inv_tau * logsigmoidf_(rg[d])) : 1.f;
+        if (lower) {
+          go[d] = rl[d] + (1.f - rl[d]) * sigmoidf_(rg[d]);
+          kv = 1.f - go[d];
+        }
+        ko[d] = kv * k_scale; qo[d] = qv * q_scale;
       }
 #pragma unroll
       for (int d4 = 0; d4 < DPT / 4; ++d4) {
@@ -385,7 +394,7 @@ decay_scan_kernel(const T* __restrict__ q, long ldq, const T* __restrict__ k, lo
     if (tid < v_items) {
       float vo[NC];
 #pragma unroll
-      for (int c = 0; c < NC; ++c) vo[c] = act ? siluf_(rv[c]) : rv[c];
+      for (int c = 0; c < NC; ++c) vo[c] = (act & 4) ? siluf_(rv[c]) : rv[c];
       reinterpret_cast<float4*>(sv)[2 * tid] = make_float4(vo[0], vo[1], vo[2], vo[3]);
       reinterpret_cast<float4*>(sv)[2 * tid + 1] = make_float4(vo[4], vo[5], vo[6], vo[7]);
     }
@@ -466,7 +475,8 @@ decay_scan_kernel(const T* __restrict__ q, long ldq, const T* __restrict__ k, lo
 // ------------------------------------------------------------------------------------------------------------------
 // Gated RMS norm of a read-out o [rows, H*V] (fp32):  y = o / sqrt(mean(o^2) + eps) * w * act(gate) * out_scale, the
 // mean taken over the V channels of every head (per_head = 1, w [V] shared by the heads or absent) or over the whole
-// row (per_head = 0, w [H*V] or absent); act 0: silu, 1: sigmoid.  One warp per (row, head), or one block per row.
+// row (per_head = 0, w [H*V] or absent); act 0: silu, 1: sigmoid, 2: no gate (the gate pointer is not read).  One warp per
+// (row, head), or one block per row.
 // ------------------------------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void gated_norm_head_kernel(const float* __restrict__ o, const T* __restrict__ gate, long ldg, const T* __restrict__ w,
@@ -482,9 +492,10 @@ __global__ void gated_norm_head_kernel(const float* __restrict__ o, const T* __r
     ss = warp_sum(ss);
     const float rv = out_scale / sqrtf(ss / (float)V + eps);
     for (int i = lane * 4; i < V; i += 128) {
-      const float4 a = *reinterpret_cast<const float4*>(orow + i), g = ld4(gate + tok * ldg + h * V + i);
+      const float4 a = *reinterpret_cast<const float4*>(orow + i), g = act == 2 ? make_float4(0.f, 0.f, 0.f, 0.f) : ld4(gate + tok * ldg + h * V + i);
       const float4 wv = w ? ld4(w + i) : make_float4(1.f, 1.f, 1.f, 1.f);
-      const float4 ga = act == 0 ? make_float4(siluf_(g.x), siluf_(g.y), siluf_(g.z), siluf_(g.w))
+      const float4 ga = act == 2 ? make_float4(1.f, 1.f, 1.f, 1.f)
+                      : act == 0 ? make_float4(siluf_(g.x), siluf_(g.y), siluf_(g.z), siluf_(g.w))
                                  : make_float4(sigmoidf_(g.x), sigmoidf_(g.y), sigmoidf_(g.z), sigmoidf_(g.w));
       st4(y + tok * ldy + h * V + i, make_float4(a.x * rv * wv.x * ga.x, a.y * rv * wv.y * ga.y, a.z * rv * wv.z * ga.z, a.w * rv * wv.w * ga.w));
     }
@@ -494,8 +505,8 @@ __global__ void gated_norm_head_kernel(const float* __restrict__ o, const T* __r
   ss = warp_sum(ss);
   const float rr = out_scale / sqrtf(ss / (float)V + eps);
   for (int i = lane; i < V; i += 32) {
-    const float g = ldf(gate + tok * ldg + h * V + i);
-    const float ga = act == 0 ? siluf_(g) : sigmoidf_(g);
+    const float g = act == 2 ? 0.f : ldf(gate + tok * ldg + h * V + i);
+    const float ga = act == 2 ? 1.f : (act == 0 ? siluf_(g) : sigmoidf_(g));
     stf(y + tok * ldy + h * V + i, orow[i] * rr * (w ? ldf(w + i) : 1.f) * ga);
   }
 }
@@ -512,9 +523,10 @@ __global__ void gated_norm_row_kernel(const float* __restrict__ o, const T* __re
     ss = block_sum(ss, red);
     const float rv = out_scale / sqrtf(ss / (float)n + eps);
     for (int i = threadIdx.x * 4; i < n; i += blockDim.x * 4) {
-      const float4 a = *reinterpret_cast<const float4*>(orow + i), g = ld4(gate + tok * ldg + i);
+      const float4 a = *reinterpret_cast<const float4*>(orow + i), g = act == 2 ? make_float4(0.f, 0.f, 0.f, 0.f) : ld4(gate + tok * ldg + i);
       const float4 wv = w ? ld4(w + i) : make_float4(1.f, 1.f, 1.f, 1.f);
-      const float4 ga = act == 0 ? make_float4(siluf_(g.x), siluf_(g.y), siluf_(g.z), siluf_(g.w))
+      const float4 ga = act == 2 ? make_float4(1.f, 1.f, 1.f, 1.f)
+                      : act == 0 ? make_float4(siluf_(g.x), siluf_(g.y), siluf_(g.z), siluf_(g.w))
                                  : make_float4(sigmoidf_(g.x), sigmoidf_(g.y), sigmoidf_(g.z), sigmoidf_(g.w));
       st4(y + tok * ldy + i, make_float4(a.x * rv * wv.x * ga.x, a.y * rv * wv.y * ga.y, a.z * rv * wv.z * ga.z, a.w * rv * wv.w * ga.w));
     }
@@ -524,8 +536,8 @@ __global__ void gated_norm_row_kernel(const float* __restrict__ o, const T* __re
   ss = block_sum(ss, red);
   const float rr = out_scale / sqrtf(ss / (float)n + eps);
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const float g = ldf(gate + tok * ldg + i);
-    const float ga = act == 0 ? siluf_(g) : sigmoidf_(g);
+    const float g = act == 2 ? 0.f : ldf(gate + tok * ldg + i);
+    const float ga = act == 2 ? 1.f : (act == 0 ? siluf_(g) : sigmoidf_(g));
     stf(y + tok * ldy + i, orow[i] * rr * (w ? ldf(w + i) : 1.f) * ga);
   }
 }
@@ -591,10 +603,11 @@ int lbl_hc_step(float* x, long rows, int n, int ns, const void* y, long ldy, int
 }
 
 int lbl_decay_scan(const void* q, long ldq, const void* k, long ldk, const void* v, long ldv, const float* decay, const float* z,
-                   long ldz, const float* zb, float inv_tau, float q_scale, float k_scale, int act, float* S, const int* seq_off,
-                   const int* slots, const int* past, float* out, int B, int H, int D, int V, int dtype, cudaStream_t s) {
+                   long ldz, const float* zb, const float* lower, float inv_tau, float q_scale, float k_scale, int act, float* S,
+                   const int* seq_off, const int* slots, const int* past, float* out, int B, int H, int D, int V, int dtype,
+                   cudaStream_t s) {
   if (B == 0) return 0;
-  if (D > 256 || (!decay && !z) || (z && !zb)) return -1;
+  if (D > 256 || (!decay && !z) || (z && !zb) || (lower && !z)) return -1;
   int dpt = D <= 64 ? 4 : 8;                    // rows per lane: 16 lanes per column group at D = 64 and at D = 128
   // few (sequence, head) pairs: the smaller tile doubles the threads per pair, which hides more of the serial walk's latency
   if (dpt == 8 && D <= 128 && (long)B * H * ((V + 127) / 128) < 100) dpt = 4;
@@ -615,10 +628,10 @@ int lbl_decay_scan(const void* q, long ldq, const void* k, long ldk, const void*
   const int esz = dtype ? 2 : 4;
   const int vec = (D % 8 == 0 && V % 8 == 0 && (ldq * esz) % 16 == 0 && (ldk * esz) % 16 == 0 && (ldv * esz) % 16 == 0 &&
                    ((uintptr_t)q & 15) == 0 && ((uintptr_t)k & 15) == 0 && ((uintptr_t)v & 15) == 0 &&
-                   (!z || (ldz % 4 == 0 && ((uintptr_t)z & 15) == 0 && ((uintptr_t)zb & 15) == 0))) ? 1 : 0;
+                   (!z || (ldz % 4 == 0 && ((uintptr_t)z & 15) == 0 && ((uintptr_t)zb & 15) == 0)) && ((uintptr_t)lower & 15) == 0) ? 1 : 0;
 #define DS(TT, P) { \
     if (smem > 48 * 1024) cudaFuncSetAttribute(decay_scan_kernel<TT, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    decay_scan_kernel<TT, P><<<grid, threads, smem, s>>>((const TT*)q, ldq, (const TT*)k, ldk, (const TT*)v, ldv, decay, z, ldz, zb, \
+    decay_scan_kernel<TT, P><<<grid, threads, smem, s>>>((const TT*)q, ldq, (const TT*)k, ldk, (const TT*)v, ldv, decay, z, ldz, zb, lower, \
         inv_tau, q_scale, k_scale, act, S, seq_off, slots, past, out, H, D, V, R, VT, CT, vec); }
   if (dtype == 0) { if (dpt == 4) DS(float, 4) else DS(float, 8) }
   else { if (dpt == 4) DS(bf16, 4) else DS(bf16, 8) }
@@ -629,6 +642,7 @@ int lbl_decay_scan(const void* q, long ldq, const void* k, long ldk, const void*
 int lbl_gated_norm(const float* o, const void* gate, long ldg, const void* w, float eps, int act, float out_scale, void* y, long ldy,
                    long rows, int H, int V, int per_head, int dtype, cudaStream_t s) {
   if (rows == 0) return 0;
+  if (act == 2) { gate = nullptr; ldg = 0; }
   const int vec = (V % 4 == 0 && ldg % 4 == 0 && ldy % 4 == 0 && ((uintptr_t)o & 15) == 0 && ((uintptr_t)gate & 15) == 0 &&
                    ((uintptr_t)y & 15) == 0 && ((uintptr_t)w & 15) == 0) ? 1 : 0;
   if (per_head) {

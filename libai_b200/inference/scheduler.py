@@ -58,7 +58,9 @@ class RequestScheduler:
         # single-token steps of a batch that stays together replay from a CUDA graph (captured at the batch's second such step)
         self.cuda_graphs = (os.environ.get("LIBAI_B200_DECODE_GRAPHS", "1") == "1") if cuda_graphs is None else cuda_graphs
         self._graphs: Dict[tuple, object] = {}
-        self.max_tokens = max_tokens          # advisory: the state of these models does not grow with the tokens held
+        self.max_tokens = max_tokens          # sizes the paged key/value pools; other state does not grow with the tokens held
+        if max_tokens:
+            self.cache.reserve(max_tokens)
         self.slot_of: Dict[Hashable, int] = {}
         self.device = model.head.device
 
@@ -75,6 +77,7 @@ class RequestScheduler:
                 self.slot_of[rid] = self.cache.allocate(1)[0]
         slots = [self.slot_of[rid] for rid, _, _ in entries]
         lens = [len(toks) for _, toks, _ in entries]
+        self.cache.prepare(slots, lens)                         # may move the buffers: before a captured graph is looked up
         if self.cuda_graphs and self.device.type == "cuda" and all(n == 1 for n in lens) and hasattr(self.model, "step_device"):
             logits = self._graphed_single_tokens(entries, slots)
             if logits is not None:

@@ -20,5 +20,6 @@ from .hyper_connections import HyperConnection
 from .latent_attention import LatentAttention
 from .layer_norm import DynamicTanh
 from .linear_attention import DecayLinearAttention
-from .moe import MoEFeedForward
+from .moe import GatedFeedForward, MoEFeedForward
+from .paged_attention import PagedAttention
 from .ring_attention import RingAttention

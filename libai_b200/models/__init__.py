@@ -7,6 +7,7 @@ from .llama_model import LlamaForCausalLM, LlamaModel
 from .resmlp import ResMLP
 from .salizen_model import SalizenForCausalLM, SalizenModel
 from .roberta_model import RobertaForCausalLM, RobertaForPreTraining, RobertaModel
+from .zubarax_model import ZubaraxForCausalLM, ZubaraxModel
 from .swin_transformer import SwinTransformer
 from .swin_transformer_v2 import SwinTransformerV2
 from .t5_model import T5ForPreTraining, T5Model
@@ -21,5 +22,5 @@ __all__ = [
     "VisionTransformer", "SwinTransformer", "SwinTransformerV2", "ResMLP",
     "LlamaModel", "LlamaForCausalLM",
     "BumodraModel", "BumodraForCausalLM", "NefelornModel", "NefelornForCausalLM",
-    "SalizenModel", "SalizenForCausalLM",
+    "SalizenModel", "SalizenForCausalLM", "ZubaraxModel", "ZubaraxForCausalLM",
 ]

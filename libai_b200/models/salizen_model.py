@@ -33,7 +33,7 @@ from torch import nn
 from libai_b200.config import configurable
 from libai_b200.inference.ragged import RaggedBatch
 from libai_b200.inference.state_cache import SequenceStateCache
-from libai_b200.layers import DecayLinearAttention, HyperConnection, MoEFeedForward, RingAttention, RMSLayerNorm
+from libai_b200.layers import DecayLinearAttention, GatedFeedForward, HyperConnection, MoEFeedForward, RingAttention, RMSLayerNorm
 from libai_b200.layers._param import create_parameter, normal_init, xavier_normal_
 from libai_b200.ops import kv_functional as KF
 from libai_b200.ops import lin_functional as LF
@@ -84,20 +84,7 @@ def mixer_parts(mix):
     return mix.parts() if isinstance(mix, ParallelMixer) else [("", mix, 1.0)]
 
 
-class GatedFF(nn.Module):
-    """``W_down (act(W_gate h) · W_up h)`` without biases; ``gate_up`` stacks the two input matrices (gate rows, then up rows)."""
-
-    def __init__(self, width, ff, act="gelu_tanh", *, layer_idx=0):
-        super().__init__()
-        self.act, self.ff = act, ff
-        self.gate_up = create_parameter((2 * ff, width), xavier_normal_, layer_idx=layer_idx)
-        self.down = create_parameter((width, ff), xavier_normal_, layer_idx=layer_idx)
-
-    def forward(self, h):
-        gu = KF.linear(h, self.gate_up)
-        a = torch.empty(h.shape[0], self.ff, dtype=h.dtype, device=h.device)
-        KF.act_rows(gu, a, KF.ACTS[self.act], gated=True)
-        return KF.linear_f32(a, self.down)
+GatedFF = GatedFeedForward          # the dense feed-forward of a block
 
 
 class HyperBlock(nn.Module):

@@ -28,7 +28,7 @@ class StatefulCausalLM(nn.Module, Generator):
     def state_cache(self) -> SequenceStateCache:
         p = self.head
         if self.state is None or self.state.device != p.device or self.state.dtype != p.dtype:
-            self.state = SequenceStateCache(p.device, p.dtype)
+            self.state = SequenceStateCache(p.device, p.dtype, page_size=getattr(self, "kv_page_size", 64))
             self._handles = self.model.register_state(self.state)
             self._gen_slots = None
         return self.state
@@ -40,6 +40,7 @@ class StatefulCausalLM(nn.Module, Generator):
         step's slots.  Returns fp32 logits of the packed rows ``logits_rows`` (default: all), ``[rows, vocab]``."""
         cache = self.state_cache()
         tokens = tokens.to(self.head.device, torch.long).contiguous()
+        cache.prepare(rb.slot_list, rb.lens)                   # pages of the positions this step writes (paged entries only)
         logits = self.step_device(tokens, rb, logits_rows, tap=tap)
         cache.advance(rb.slot_list, rb.lens)
         return logits

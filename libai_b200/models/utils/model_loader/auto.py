@@ -42,16 +42,25 @@ def _salizen():
     return SalizenForCausalLM, SalizenLoader, {}
 
 
+def _zubarax():
+    from libai_b200.models import ZubaraxForCausalLM
+    from .zubarax_loader import ZubaraxLoader
+
+    return ZubaraxForCausalLM, ZubaraxLoader, {}
+
+
 ARCHITECTURES = {
     "bumodra": _bumodra,
     "nefelorn": _nefelorn,
     "salizen": _salizen,
+    "zubarax": _zubarax,
     "llama": _llama, "llamaforcausallm": _llama,
 }
 
 
 # native libraries (``libai_b200.ops.build``) that a model's generation path launches besides the GEMM library ``_C``
-NATIVE_LIBS = {"bumodra": ["_C_seq"], "nefelorn": ["_C_kv"], "salizen": ["_C_kv", "_C_lin"]}
+NATIVE_LIBS = {"bumodra": ["_C_seq"], "nefelorn": ["_C_kv"], "salizen": ["_C_kv", "_C_lin"],
+               "zubarax": ["_C_kv", "_C_lin"]}
 
 
 def native_libs_of(path: str, dtype=torch.bfloat16):

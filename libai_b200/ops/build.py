@@ -1,6 +1,6 @@
 """In-tree build of the native extensions: ``libai_b200/_C.so`` (GEMM, attention, norms, optimizer, collectives) and
-``libai_b200/_C_seq.so`` (ragged-batch sequence mixers with per-sequence state), ``libai_b200/_C_kv.so`` (ring key/value
-caches, masked grouped-query attention, Dynamic-Tanh norms, mixture of experts) and ``libai_b200/_C_lin.so`` (bigram embedding,
+``libai_b200/_C_seq.so`` (ragged-batch sequence mixers with per-sequence state), ``libai_b200/_C_kv.so`` (ring and paged key/value
+caches, masked grouped-query attention, attention with mixed heads, Dynamic-Tanh and post-norm residuals, mixture of experts) and ``libai_b200/_C_lin.so`` (bigram embedding,
 hyper-connection streams, decayed linear-attention recurrences).
 
     python -m libai_b200.ops.build [--force] [--verbose] [--only _C|_C_seq|_C_kv|_C_lin]
@@ -31,7 +31,7 @@ SEQ_SO_PATH = os.path.join(ROOT, "_C_seq.so")
 SEQ_CU_SOURCES = ["seq_mixers.cu"]
 SEQ_CPP_SOURCES = ["seq_bindings.cpp"]
 KV_SO_PATH = os.path.join(ROOT, "_C_kv.so")
-KV_CU_SOURCES = ["kv_mixers.cu"]
+KV_CU_SOURCES = ["kv_mixers.cu", "paged_mixers.cu"]
 KV_CPP_SOURCES = ["kv_bindings.cpp"]
 LIN_SO_PATH = os.path.join(ROOT, "_C_lin.so")
 LIN_CU_SOURCES = ["lin_mixers.cu"]

@@ -17,8 +17,9 @@ import torch.nn.functional as F
 from . import count_launch, impl, load_kv_ext
 from .seq_functional import _tcgen05_gemm, linear, linear_accumulate  # noqa: F401  (projections are shared)
 
-ACT_COPY, ACT_GELU, ACT_SILU, ACT_GELU_TANH, ACT_RELU2 = 0, 1, 2, 3, 4
-ACTS = {"copy": ACT_COPY, "gelu": ACT_GELU, "silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH, "relu2": ACT_RELU2}
+ACT_COPY, ACT_GELU, ACT_SILU, ACT_GELU_TANH, ACT_RELU2, ACT_SWISH_CLAMP = 0, 1, 2, 3, 4, 5
+ACTS = {"copy": ACT_COPY, "gelu": ACT_GELU, "silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH, "relu2": ACT_RELU2,
+        "swish_clamp": ACT_SWISH_CLAMP}
 
 
 def _native(t: torch.Tensor) -> bool:
@@ -35,6 +36,15 @@ def _act(v, act: int):
     if act == ACT_RELU2:
         return torch.relu(v) ** 2
     return v
+
+
+def _gated_pair(g, u, act: int, limit: float = 0.0):
+    """A gated pair: ``act(g) · u``, or — ``ACT_SWISH_CLAMP`` — ``g' · sigmoid(1.702 g') · (u' + 1)`` with ``g' = min(g, limit)`` and
+    ``u' = clamp(u, −limit, limit)``."""
+    if act == ACT_SWISH_CLAMP:
+        g, u = g.clamp(max=limit), u.clamp(-limit, limit)
+        return g * torch.sigmoid(1.702 * g) * (u + 1.0)
+    return _act(g, act) * u
 
 
 # ------------------------------------------------------------------------------------------------------------ projections
@@ -100,16 +110,15 @@ def dyt_residual(x, y=None, post=None, nxt=None, h=None, pos=None, cw=None):
     return x
 
 
-def act_rows(inp, out, act: int, gated: bool = False):
-    """``out = act(inp)``, or — ``gated`` — ``out = act(inp[:, :n]) · inp[:, n:]`` (column slices of row-major matrices)."""
+def act_rows(inp, out, act: int, gated: bool = False, limit: float = 0.0):
+    """``out = act(inp)``, or — ``gated`` — ``out = act(inp[:, :n]) · inp[:, n:]`` (column slices of row-major matrices;
+    ``ACT_SWISH_CLAMP`` is gated only and takes ``limit``, see :func:`_gated_pair`)."""
     if _native(inp):
         count_launch()
-        load_kv_ext().act_rows(inp, out, act, gated)
+        load_kv_ext().act_rows(inp, out, act, gated, float(limit))
         return out
     n = out.shape[1]
-    v = _act(inp[:, :n].float(), act)
-    if gated:
-        v = v * inp[:, n:].float()
+    v = _gated_pair(inp[:, :n].float(), inp[:, n:].float(), act, limit) if gated else _act(inp[:, :n].float(), act)
     out.copy_(v)
     return out
 
@@ -327,13 +336,14 @@ def ring_attention(q, ring, first, gate, rb, y, H: int, G: int, D: int, V: int, 
 
 
 # ------------------------------------------------------------------------------------------------------ mixture of experts
-ROUTE_SIGMOID, ROUTE_SOFTMAX = 0, 1
+ROUTE_SIGMOID, ROUTE_SOFTMAX, ROUTE_SIGMOID_RAW = 0, 1, 2
 
 
 def moe_route(h, wr, top: int, rscale: float, counts=None, bias=None, mode: int = ROUTE_SIGMOID):
     """Router on the fp32 logits ``z = W_r h`` (``+ bias``, fp32 ``[E]``).  ``ROUTE_SIGMOID``: the ``top`` largest
     ``s = sigmoid(z)``, weights ``s / (Σ s + 1e-20) · rscale``; ``ROUTE_SOFTMAX``: the ``top`` largest logits, weights = softmax
-    over the chosen logits only, times ``rscale``.  Ties go to the lower index.  Returns ``idx`` int32 and ``wts`` fp32, both
+    over the chosen logits only, times ``rscale``; ``ROUTE_SIGMOID_RAW``: the ``top`` largest ``s = sigmoid(z)``, weights
+    ``s · rscale`` (not normalised).  Ties go to the lower index.  Returns ``idx`` int32 and ``wts`` fp32, both
     ``[tokens, top]``; ``counts`` (int32 ``[E]``, zeroed by the caller) receives the number of tokens of every expert."""
     T = h.shape[0]
     idx = torch.empty(T, top, dtype=torch.int32, device=h.device)
@@ -351,7 +361,7 @@ def moe_route(h, wr, top: int, rscale: float, counts=None, bias=None, mode: int 
         w = torch.softmax(tv, -1) * rscale
     else:
         tv, ti = torch.sigmoid(z).topk(top, -1)
-        w = tv / (tv.sum(-1, keepdim=True) + 1e-20) * rscale
+        w = tv * rscale if mode == ROUTE_SIGMOID_RAW else tv / (tv.sum(-1, keepdim=True) + 1e-20) * rscale
     idx.copy_(ti)
     wts.copy_(w)
     if counts is not None:
@@ -373,33 +383,36 @@ def router_logits(h, wr):
     return F.linear(h.float(), wr.float())
 
 
-def moe_pairs(h, wgu, wd, idx, wts, act: int):
+def moe_pairs(h, wgu, wd, idx, wts, act: int, limit: float = 0.0, weight_input: bool = False):
     """Experts for few tokens: every (token, chosen expert) pair reads its expert's matrices.  ``wgu`` ``[E, 2·ff, width]``
     (gate rows, then up rows), ``wd`` ``[E, width, ff]``.  Returns ``Σ_k wts[t,k] · W_down,k (act(W_gate,k h) · W_up,k h)`` as
-    fp32 ``[tokens, width]``."""
+    fp32 ``[tokens, width]``; with ``weight_input`` the weight multiplies the expert's input instead (``wts[t,k] · h`` rounded to
+    the compute dtype) and the outputs are summed."""
     T, n = h.shape
     top, ff = idx.shape[1], wgu.shape[1] // 2
     out = torch.empty(T, n, dtype=torch.float32, device=h.device)
     if _native(h):
         count_launch(2)
         a = torch.empty(T * top, ff, dtype=h.dtype, device=h.device)
-        load_kv_ext().moe_pairs(h, wgu, wd, idx, wts, a, out, act)
+        load_kv_ext().moe_pairs(h, wgu, wd, idx, wts, a, out, act, float(limit), bool(weight_input))
         return out
     for t in range(T):
         acc = torch.zeros(n)
         for k in range(top):
             e = int(idx[t, k])
-            gu = wgu[e].float() @ h[t].float()
-            a = (_act(gu[:ff], act) * gu[ff:]).to(h.dtype).float()
-            acc += wts[t, k] * (wd[e].float() @ a)
+            hin = (wts[t, k] * h[t].float()).to(h.dtype).float() if weight_input else h[t].float()
+            gu = wgu[e].float() @ hin
+            a = _gated_pair(gu[:ff], gu[ff:], act, limit).to(h.dtype).float()
+            acc += (1.0 if weight_input else wts[t, k]) * (wd[e].float() @ a)
         out[t] = acc
     return out
 
 
-def moe_sorted(h, wgu, wd, idx, counts, act: int):
+def moe_sorted(h, wgu, wd, idx, counts, act: int, limit: float = 0.0, in_wts=None):
     """Experts for many tokens: the rows are copied into a matrix sorted by expert, every expert runs as two dense products on
     its row range, and the caller gathers the weighted sum (:func:`dyt_residual` with ``pos``).  Returns
-    ``(ys fp32 [rows, width], pos int32 [tokens, top])``: the output row of pair (t, k) is ``ys[pos[t, k]]``.
+    ``(ys fp32 [rows, width], pos int32 [tokens, top])``: the output row of pair (t, k) is ``ys[pos[t, k]]``.  With ``in_wts``
+    (fp32 ``[tokens, top]``) the copied row of pair (t, k) is ``in_wts[t, k] · h[t]``: routing weights on the experts' inputs.
 
     bf16 on the GPU: every expert's range starts on a multiple of 128 rows and each product is ONE launch of the tcgen05 GEMM
     in its grouped mode (the expert of every 128-row block is a device-side list), so nothing is read back by the host and the
@@ -417,11 +430,11 @@ def moe_sorted(h, wgu, wd, idx, counts, act: int):
         meta = torch.empty(2 * E + 1 + rows // 128, dtype=torch.int32, device=dev)
         groups = meta[2 * E + 1:]
         count_launch(5)
-        load_kv_ext().moe_sort(h, idx, counts, meta[: E + 1], meta[E + 1: 2 * E + 1], pos, xs, 128, groups)
+        load_kv_ext().moe_sort(h, idx, counts, meta[: E + 1], meta[E + 1: 2 * E + 1], pos, xs, 128, groups, in_wts)
         gu = torch.empty(rows, 2 * ff, dtype=h.dtype, device=dev)
         load_ext().gemm_grouped_blocks(xs, wgu.detach(), groups, gu)
         a = torch.empty(rows, ff, dtype=h.dtype, device=dev)
-        act_rows(gu, a, act, gated=True)
+        act_rows(gu, a, act, gated=True, limit=limit)
         ys = torch.empty(rows, n, dtype=torch.float32, device=dev)
         load_ext().gemm_grouped_blocks(a, wd.detach(), groups, ys)
         return ys, pos
@@ -429,18 +442,18 @@ def moe_sorted(h, wgu, wd, idx, counts, act: int):
     if _native(h):
         count_launch(2)
         meta = torch.empty(2 * E + 1, dtype=torch.int32, device=dev)
-        load_kv_ext().moe_sort(h, idx, counts, meta[: E + 1], meta[E + 1:], pos, xs, 1, None)
+        load_kv_ext().moe_sort(h, idx, counts, meta[: E + 1], meta[E + 1:], pos, xs, 1, None, in_wts)
         cnt = counts.tolist()
     else:
         order = torch.sort(idx.reshape(-1).long(), stable=True).indices
         pos.view(-1)[order] = torch.arange(P, dtype=torch.int32)
-        xs.copy_(h[order // top])
+        xs.copy_(h[order // top] if in_wts is None else in_wts.reshape(-1)[order][:, None] * h[order // top].float())
         cnt = torch.bincount(idx.reshape(-1).long(), minlength=E).tolist()
     gu = torch.empty(P, 2 * ff, dtype=h.dtype, device=dev)
     a = torch.empty(P, ff, dtype=h.dtype, device=dev)
     ys = torch.empty(P, n, dtype=torch.float32, device=dev)
     _grouped_products(xs, wgu, cnt, gu, False)
-    act_rows(gu, a, act, gated=True)
+    act_rows(gu, a, act, gated=True, limit=limit)
     _grouped_products(a, wd, cnt, ys, False)
     return ys, pos
 

@@ -13,7 +13,8 @@ import torch.nn.functional as F
 
 from . import count_launch, impl, load_lin_ext
 
-GATE_SILU, GATE_SIGMOID = 0, 1
+GATE_SILU, GATE_SIGMOID, GATE_NONE = 0, 1, 2
+ACT_Q, ACT_K, ACT_V = 1, 2, 4          # which of q, k, v pass through SiLU in decay_scan
 
 
 def _native(t: torch.Tensor) -> bool:
@@ -70,29 +71,42 @@ def hc_step(x, y=None, post=None, nxt=None, h=None, pos=None, cw=None, eps: floa
 
 # ------------------------------------------------------------------------------------------------------- decayed recurrence
 def decay_scan(q, k, v, S, rb, *, decay=None, z=None, zb=None, tau: float = 1.0, q_scale: float = 1.0, k_scale: float = 1.0,
-               act: bool = False):
+               act=False, lower=None):
     """Linear attention with a decay over the packed rows: per head ``S ← diag(a_t) S + k_t v_tᵀ``, ``o_t = Sᵀ q_t``.
 
-    ``q``, ``k`` ``[tokens, H·D]`` and ``v`` ``[tokens, H·V]`` may be column slices of one projection output; ``act`` passes all
-    three through SiLU; ``q`` is multiplied by ``q_scale`` and ``k`` by ``k_scale``.  The decay is either ``decay`` (fp32 ``[H]``,
-    one fixed number per head) or, per token and key channel, ``sigmoid(z + zb)^(1/tau)`` from the fp32 logits ``z``
-    ``[tokens, H·D]`` and their bias ``zb`` ``[H·D]``.  ``S`` ``[slots, H, D, V]`` fp32 is read (unless ``past == 0``) and left at
+    ``q``, ``k`` ``[tokens, H·D]`` and ``v`` ``[tokens, H·V]`` may be column slices of one projection output; ``act`` says which of
+    them pass through SiLU (``True``: all three, or a sum of ``ACT_Q``, ``ACT_K``, ``ACT_V``); ``q`` is multiplied by ``q_scale`` and
+    ``k`` by ``k_scale``.  The decay is either ``decay`` (fp32 ``[H]``, one fixed number per head) or, per token and key channel,
+    ``sigmoid(z + zb)^(1/tau)`` from the fp32 logits ``z`` ``[tokens, H·D]`` and their bias ``zb`` ``[H·D]``.  With ``lower`` (fp32
+    ``[H·D]``) the decay is ``a = lower + (1 − lower) · sigmoid(z + zb)`` and the written key is ``1 − a`` (``k`` is ignored and may
+    be ``None``): a forget gate bounded from below that also decides what is written.  ``S`` ``[slots, H, D, V]`` fp32 is read (unless ``past == 0``) and left at
     the state after the last row.  Returns the read-outs ``[tokens, H·V]`` in fp32."""
     H, D, V = S.shape[1], S.shape[2], S.shape[3]
     out = torch.empty(q.shape[0], H * V, dtype=torch.float32, device=q.device)
+    act = 7 if act is True else int(act)
     if _native(q):
         count_launch()
-        load_lin_ext().decay_scan(q, k, v, decay, z, zb, 1.0 / float(tau), float(q_scale), float(k_scale), bool(act), S, rb.seq_off,
-                                  rb.slots, rb.past, out)
+        load_lin_ext().decay_scan(q, q if k is None else k, v, decay, z, zb, 1.0 / float(tau), float(q_scale), float(k_scale), act, S,
+                                  rb.seq_off, rb.slots, rb.past, out, lower)
         return out
     for b in range(rb.B):
         lo, n, slot = rb.offsets[b], rb.lens[b], rb.slot_list[b]
         st = S[slot].clone() if rb.past_list[b] > 0 else torch.zeros(H, D, V, device=q.device)
-        qq, kk, vv = q[lo:lo + n].float(), k[lo:lo + n].float(), v[lo:lo + n].float()
-        if act:
-            qq, kk, vv = F.silu(qq), F.silu(kk), F.silu(vv)
+        qq, vv = q[lo:lo + n].float(), v[lo:lo + n].float()
+        kk = k[lo:lo + n].float() if lower is None else None
+        if act & ACT_Q:
+            qq = F.silu(qq)
+        if act & ACT_K and kk is not None:
+            kk = F.silu(kk)
+        if act & ACT_V:
+            vv = F.silu(vv)
+        if lower is not None:
+            a = (lower.float() + (1.0 - lower.float()) * torch.sigmoid(z[lo:lo + n].float() + zb.float())).view(n, H, D)
+            kk = (1.0 - a).reshape(n, H * D)
         qq, kk, vv = (qq * q_scale).view(n, H, D), (kk * k_scale).view(n, H, D), vv.view(n, H, V)
-        if z is not None:
+        if lower is not None:
+            pass
+        elif z is not None:
             a = torch.exp(F.logsigmoid(z[lo:lo + n].float() + zb.float()) / tau).view(n, H, D)
         else:
             a = decay.float()[None, :, None].expand(n, H, D)
@@ -106,15 +120,17 @@ def decay_scan(q, k, v, S, rb, *, decay=None, z=None, zb=None, tau: float = 1.0,
 def gated_norm(o, gate, w, eps: float, act: int, y, H: int, V: int, *, per_head: bool, out_scale: float = 1.0):
     """``y = o / sqrt(mean(o²) + eps) · w · act(gate) · out_scale`` for the fp32 read-outs ``o`` ``[rows, H·V]``; the mean runs
     over the ``V`` channels of every head (``per_head``; ``w`` ``[V]`` shared by the heads) or over the whole row (``w``
-    ``[H·V]``); ``w = None`` leaves the weight out; ``act``: ``GATE_SILU`` or ``GATE_SIGMOID``."""
+    ``[H·V]``); ``w = None`` leaves the weight out; ``act``: ``GATE_SILU``, ``GATE_SIGMOID`` or ``GATE_NONE`` (no gate: ``gate`` may be
+    ``None``)."""
     if _native(o):
         count_launch()
         load_lin_ext().gated_norm(o, gate, w, float(eps), int(act), float(out_scale), y, H, V, bool(per_head))
         return y
     of = o.view(-1, H, V) if per_head else o.view(-1, 1, H * V)
-    g = gate.float().reshape(of.shape)
-    g = F.silu(g) if act == GATE_SILU else torch.sigmoid(g)
-    v = of * torch.rsqrt(of.pow(2).mean(-1, keepdim=True) + eps) * g * out_scale
+    v = of * torch.rsqrt(of.pow(2).mean(-1, keepdim=True) + eps) * out_scale
+    if act != GATE_NONE:
+        g = gate.float().reshape(of.shape)
+        v = v * (F.silu(g) if act == GATE_SILU else torch.sigmoid(g))
     if w is not None:
         v = v * w.float()
     y.copy_(v.reshape(-1, H * V))
