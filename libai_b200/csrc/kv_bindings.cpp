@@ -52,6 +52,9 @@ int lbp_conv_qkv_prepare(const void* qin, const void* kin, const void* vin, long
                          const int* seq_off, const int* slots, const int* past, long tokens, int B, int H, int G, int D, int V,
                          int dtype, cudaStream_t s);
 int lbp_talk_attention_tiles(int qt_max, int H, int G, int D, int V, int* kt_out);
+int lbp_talk_attention_mma(const void* q, long ldq, const void* pool, const int* table, int max_pages, int page_size, const float* talk,
+                           const float* sink, const int* qt_seq, const int* qt_start, int ntiles, const int* seq_off, const int* slots,
+                           const int* past, void* y, long ldy, int H, int G, int D, int V, float scale, float out_scale, cudaStream_t s);
 int lbp_talk_attention(const void* q, long ldq, const void* pool, const int* table, int max_pages, int page_size, const float* talk,
                        const float* sink, const int* qt_seq, const int* qt_start, int ntiles, int QT, int KT, const int* seq_off,
                        const int* slots, const int* past, void* y, long ldy, float* part, int nparts, long rows, int H, int G, int D,
@@ -395,6 +398,15 @@ void talk_attention(const Tensor& q, const Tensor& pool, const Tensor& table, co
   const float* tp = nullptr; const float* sp = nullptr; float* pp = nullptr;
   if (has(talk)) { TORCH_CHECK(talk->is_cuda() && talk->scalar_type() == at::kFloat && talk->is_contiguous() && talk->numel() == H * H, "talk_attention: talk fp32 [H, H]"); tp = talk->data_ptr<float>(); }
   if (has(sink)) { TORCH_CHECK(sink->is_cuda() && sink->scalar_type() == at::kFloat && sink->is_contiguous() && sink->numel() == H, "talk_attention: sink fp32 [H]"); sp = sink->data_ptr<float>(); }
+  if (QT == 16) {                               // the tensor-core prompt tiling (bf16; the launcher refuses sizes it is not built for)
+    TORCH_CHECK(dtype == 1 && nparts == 1, "talk_attention: tiles of 16 queries are the bf16 tensor-core form");
+    c10::cuda::CUDAGuard guard(q.device());
+    check(lbp_talk_attention_mma(q.data_ptr(), q.stride(0), pool.data_ptr(), meta(table), (int)table.size(1), (int)pool.size(1), tp, sp,
+                                 meta(qt_seq), meta(qt_start), (int)qt_seq.numel(), meta(seq_off), meta(slots), meta(past), y.data_ptr(),
+                                 y.stride(0), (int)H, (int)G, (int)D, (int)V, (float)scale, (float)out_scale, cur_stream()),
+          "talk_attention (tensor cores)");
+    return;
+  }
   if (nparts > 1) {
     TORCH_CHECK(has(part) && part->is_cuda() && part->scalar_type() == at::kFloat && part->is_contiguous() && part->numel() >= rows * nparts * H * (V + 2), "talk_attention: part fp32 [rows, nparts, H, V + 2]");
     pp = part->data_ptr<float>();

@@ -331,6 +331,224 @@ talk_attention_kernel(const T* __restrict__ q, long ldq, const T* __restrict__ p
   }
 }
 
+// ------------------------------------------------------------------------------------------------------------------
+// Tensor-core form of the prompt tiling for bf16 with equal key and value head sizes DH (mma.m16n8k16, ldmatrix,
+// cp.async).  A block takes 16 consecutive queries of one sequence and all heads, one warp per head, 32 keys at a time:
+//   1  warp h: raw scores Q_h K^T of its head on the tensor cores, times scale, as fp32 into shared memory;
+//   2  the mix over heads on the fp32 pipe: warp w takes HB output heads and 16 / HB of the rows, lane = key, the rows of
+//      `talk` of its heads in registers, so that a loaded raw score feeds HB multiply-adds; causal mask; online softmax (the
+//      running maximum and sum of the warp's 16 (head, row) pairs live in lanes 0..15); probabilities as bf16 and the
+//      correction factors into shared memory;
+//   3  warp h: O_h <- O_h * correction + P_h V on the tensor cores, O in registers.
+// The key tile of the next step is fetched (cp.async) while 2 and 3 run, the value tile of this step while 1 and 2 run.
+// HP is the head count padded to 8 or 16 (the size of the register arrays); QREG keeps a head's query fragments in registers.
+// ------------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" :: "r"(a), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" :: "n"(N)); }
+
+constexpr int TM_Q = 16, TM_K = 32, TM_SRS = TM_K + 8;           // queries, keys per tile; row stride of the fp32 scores
+
+template <int DH, int HP, int HB, bool QREG>
+__global__ void __launch_bounds__(HP * 32, 1)
+talk_attention_mma_kernel(const bf16* __restrict__ q, long ldq, const bf16* __restrict__ pool, const int* __restrict__ table,
+                          int max_pages, int page_size, const float* __restrict__ talk, const float* __restrict__ sink,
+                          const int* __restrict__ qt_seq, const int* __restrict__ qt_start, const int* __restrict__ seq_off,
+                          const int* __restrict__ slots, const int* __restrict__ past, bf16* __restrict__ y, long ldy, int H, int G,
+                          float scale, float out_scale) {
+  extern __shared__ __align__(16) unsigned char smraw[];
+  constexpr int KS = DH / 16, NT = DH / 8, RPW = TM_Q / HB;
+  const int GD = G * DH, C = 2 * GD, rep = H / G;
+  const int KRS = GD + 8;                       // bf16 elements per row of the key / value tiles
+  const int QRS = H * DH + 8;
+  constexpr int PRS = TM_K + 8;
+  bf16* Ks = reinterpret_cast<bf16*>(smraw);
+  bf16* Vs = Ks + TM_K * KRS;
+  bf16* Qs = Vs + TM_K * KRS;
+  bf16* Ps = Qs + TM_Q * QRS;                   // [H][16][PRS]
+  float* S0 = reinterpret_cast<float*>(Ps + H * TM_Q * PRS);   // [H][16][TM_SRS]
+  float* Cs = S0 + H * TM_Q * TM_SRS;           // [H][16] correction of this tile, then the final maximum
+  float* Ls = Cs + H * TM_Q;                    // [H][16] final sum
+  const int tid = threadIdx.x, nth = blockDim.x, warp = tid >> 5, lane = tid & 31;
+  const int b = qt_seq[blockIdx.x], t0 = qt_start[blockIdx.x];
+  const int s0 = seq_off[b], nq = min(TM_Q, seq_off[b + 1] - s0 - t0), pos0 = past[b] + t0;
+  const long row0 = s0 + t0;
+  const long slot = slots[b];
+  const int kend = pos0 + nq;
+  const int h = warp, kvh = h / rep;
+
+  auto load_rows = [&](bf16* dst, int k0, int coff) {            // 32 cache rows, columns [coff, coff + GD), 16 bytes per copy
+    const int per = GD / 8;
+    for (int i = tid; i < TM_K * per; i += nth) {
+      const int j = i / per, c = (i - j * per) * 8;
+      const int kp = k0 + j;
+      if (kp < kend) {
+        const bf16* rowp = pool + ((long)table[slot * max_pages + kp / page_size] * page_size + kp % page_size) * (long)C + coff;
+        cp_async16(dst + j * KRS + c, rowp + c);
+      } else {
+        *reinterpret_cast<uint4*>(dst + j * KRS + c) = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+  };
+  load_rows(Ks, 0, 0);
+  cp_async_commit();
+  {
+    const int per = H * DH / 8;
+    for (int i = tid; i < TM_Q * per; i += nth) {
+      const int r = i / per, c = (i - r * per) * 8;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (r < nq) v = *reinterpret_cast<const uint4*>(q + (row0 + r) * ldq + c);
+      *reinterpret_cast<uint4*>(Qs + r * QRS + c) = v;
+    }
+  }
+  // phase-2 role of this warp: heads grp * HB .. + HB - 1, rows rs * RPW .. + RPW - 1; lane r < 16 keeps the statistics of
+  // (head grp * HB + r / RPW, row rs * RPW + r % RPW)
+  const int grp = warp / HB, rs = warp % HB;
+  float Tr[HB][HP];
+#pragma unroll
+  for (int bb = 0; bb < HB; ++bb)
+#pragma unroll
+    for (int g = 0; g < HP; ++g) {
+      const int hh = grp * HB + bb;
+      Tr[bb][g] = (g < H && hh < H) ? (talk ? talk[hh * H + g] : (g == hh ? 1.f : 0.f)) : 0.f;
+    }
+  float m_reg = -INFINITY, l_reg = 0.f;
+  float o[NT][4];
+#pragma unroll
+  for (int n = 0; n < NT; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+  uint32_t qf[QREG ? KS : 1][4];
+  __syncthreads();
+  if (QREG) {
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks)
+      ldsm_x4(qf[QREG ? ks : 0], Qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * QRS + h * DH + ks * 16 + 8 * (lane >> 4));
+  }
+
+  for (int k0 = 0; k0 < kend; k0 += TM_K) {
+    cp_async_wait<0>();
+    __syncthreads();                            // keys of this step have landed; everybody is done with the last step's V and P
+    load_rows(Vs, k0, GD);
+    cp_async_commit();
+    // 1: raw scores of head h
+#pragma unroll
+    for (int np = 0; np < TM_K / 16; ++np) {
+      float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        uint32_t a[4], bk[4];
+        if (QREG) { a[0] = qf[QREG ? ks : 0][0]; a[1] = qf[QREG ? ks : 0][1]; a[2] = qf[QREG ? ks : 0][2]; a[3] = qf[QREG ? ks : 0][3]; }
+        else ldsm_x4(a, Qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * QRS + h * DH + ks * 16 + 8 * (lane >> 4));
+        ldsm_x4(bk, Ks + (np * 16 + (lane & 7) + 8 * (lane >> 4)) * KRS + kvh * DH + ks * 16 + 8 * ((lane >> 3) & 1));
+        mma_bf16(c0, a, bk[0], bk[1]);
+        mma_bf16(c1, a, bk[2], bk[3]);
+      }
+      float* sr = S0 + (h * TM_Q + (lane >> 2)) * TM_SRS + np * 16 + 2 * (lane & 3);
+      *reinterpret_cast<float2*>(sr) = make_float2(c0[0] * scale, c0[1] * scale);
+      *reinterpret_cast<float2*>(sr + 8 * TM_SRS) = make_float2(c0[2] * scale, c0[3] * scale);
+      *reinterpret_cast<float2*>(sr + 8) = make_float2(c1[0] * scale, c1[1] * scale);
+      *reinterpret_cast<float2*>(sr + 8 * TM_SRS + 8) = make_float2(c1[2] * scale, c1[3] * scale);
+    }
+    __syncthreads();                            // all raw scores are there; the key tile is free
+    if (k0 + TM_K < kend) load_rows(Ks, k0 + TM_K, 0);
+    cp_async_commit();
+    // 2: mix, mask, online softmax
+    if (grp * HB < H) {
+      const int kp = k0 + lane;
+      for (int rl = 0; rl < RPW; ++rl) {
+        const int i = rs * RPW + rl;
+        float acc[HB];
+#pragma unroll
+        for (int bb = 0; bb < HB; ++bb) acc[bb] = 0.f;
+#pragma unroll
+        for (int g = 0; g < HP; ++g) {
+          if (g < H) {
+            const float sv = S0[(g * TM_Q + i) * TM_SRS + lane];
+#pragma unroll
+            for (int bb = 0; bb < HB; ++bb) acc[bb] += Tr[bb][g] * sv;
+          }
+        }
+        const bool seen = i < nq && kp < kend && kp <= pos0 + i;
+#pragma unroll
+        for (int bb = 0; bb < HB; ++bb) {
+          const int hh = grp * HB + bb, r = bb * RPW + rl;
+          const float v = seen ? acc[bb] : -INFINITY;
+          const float mx = warp_max(v);
+          const float mo = __shfl_sync(0xffffffffu, m_reg, r);
+          const float mn = fmaxf(mo, mx);
+          const float pj = mn == -INFINITY ? 0.f : expf(v - mn);
+          const float sum = warp_sum(pj);
+          const float corr = mo == -INFINITY ? 0.f : expf(mo - mn);
+          if (lane == r) { m_reg = mn; l_reg = l_reg * corr + sum; }
+          if (hh < H) {
+            Ps[(hh * TM_Q + i) * PRS + lane] = __float2bfloat16_rn(pj);
+            if (lane == 0) Cs[hh * TM_Q + i] = corr;
+          }
+        }
+      }
+    }
+    cp_async_wait<1>();                         // the value tile (the key tile of the next step may still be in flight)
+    __syncthreads();
+    // 3: O_h <- O_h * corr + P_h V
+    {
+      const float ca = Cs[h * TM_Q + (lane >> 2)], cb = Cs[h * TM_Q + (lane >> 2) + 8];
+#pragma unroll
+      for (int n = 0; n < NT; ++n) { o[n][0] *= ca; o[n][1] *= ca; o[n][2] *= cb; o[n][3] *= cb; }
+#pragma unroll
+      for (int ks = 0; ks < TM_K / 16; ++ks) {
+        uint32_t a[4];
+        ldsm_x4(a, Ps + (h * TM_Q + (lane & 7) + 8 * ((lane >> 3) & 1)) * PRS + ks * 16 + 8 * (lane >> 4));
+#pragma unroll
+        for (int n2 = 0; n2 < NT / 2; ++n2) {
+          uint32_t bv[4];
+          ldsm_x4_t(bv, Vs + (ks * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * KRS + kvh * DH + n2 * 16 + 8 * (lane >> 4));
+          mma_bf16(o[2 * n2], a, bv[0], bv[1]);
+          mma_bf16(o[2 * n2 + 1], a, bv[2], bv[3]);
+        }
+      }
+    }
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+  if (grp * HB < H && lane < TM_Q) {            // the statistics go to the warps that hold O
+    const int hh = grp * HB + lane / RPW, i = rs * RPW + lane % RPW;
+    if (hh < H) { Cs[hh * TM_Q + i] = m_reg; Ls[hh * TM_Q + i] = l_reg; }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int i = (lane >> 2) + 8 * half;
+    if (i < nq) {
+      const float m = Cs[h * TM_Q + i];
+      float l = Ls[h * TM_Q + i], e = 1.f;
+      if (sink) {
+        const float mm = fmaxf(m, sink[h]);
+        e = expf(m - mm);
+        l = l * e + expf(sink[h] - mm);
+      }
+      const float f = e / l * out_scale;
+      bf16* dst = y + (row0 + i) * ldy + h * DH + 2 * (lane & 3);
+#pragma unroll
+      for (int n = 0; n < NT; ++n)
+        *reinterpret_cast<__nv_bfloat162*>(dst + n * 8) = __floats2bfloat162_rn(o[n][2 * half] * f, o[n][2 * half + 1] * f);
+    }
+  }
+}
+
 // one warp per (row, head): the parts' (maximum, sum, O) and the sink -> y
 template <typename T>
 __global__ void talk_attention_merge_kernel(const float* __restrict__ part, const float* __restrict__ sink, T* __restrict__ y, long ldy,
@@ -447,6 +665,34 @@ int lbp_talk_attention(const void* q, long ldq, const void* pool, const int* tab
     if (dtype) talk_attention_merge_kernel<bf16><<<mg, 256, 0, s>>>(part, sink, (bf16*)y, ldy, rows, nparts, H, V, out_scale);
     else talk_attention_merge_kernel<float><<<mg, 256, 0, s>>>(part, sink, (float*)y, ldy, rows, nparts, H, V, out_scale);
   }
+  LAUNCH_END();
+}
+
+// tensor-core prompt kernel: bf16, equal key and value head sizes of 64 or 128, at most 16 heads; -1 otherwise
+int lbp_talk_attention_mma(const void* q, long ldq, const void* pool, const int* table, int max_pages, int page_size, const float* talk,
+                           const float* sink, const int* qt_seq, const int* qt_start, int ntiles, const int* seq_off, const int* slots,
+                           const int* past, void* y, long ldy, int H, int G, int D, int V, float scale, float out_scale, cudaStream_t s) {
+  if (ntiles == 0) return 0;
+  if (D != V || (D != 64 && D != 128) || H < 1 || H > 16 || H % G != 0 || ldq % 8 != 0 || ldy % 2 != 0 ||
+      ((uintptr_t)q & 15) != 0 || ((uintptr_t)pool & 15) != 0 || ((uintptr_t)y & 3) != 0) return -1;
+  const int hp = H <= 8 ? 8 : 16;
+  const int hb = (hp == 8 && H % 4 == 0) ? 4 : ((hp == 16 && H % 2 == 0) ? 2 : 1);
+  const int GD = G * D;
+  const size_t smem = (size_t)2 * (2 * TM_K * (GD + 8) + TM_Q * (H * D + 8) + H * TM_Q * (TM_K + 8)) +
+                      (size_t)4 * (H * TM_Q * TM_SRS + 2 * H * TM_Q);
+  if (smem > 220 * 1024) return -1;
+#define TM(DH_, HP_, HB_, QR_) { \
+    cudaFuncSetAttribute(talk_attention_mma_kernel<DH_, HP_, HB_, QR_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    talk_attention_mma_kernel<DH_, HP_, HB_, QR_><<<(unsigned)ntiles, H * 32, smem, s>>>((const bf16*)q, ldq, (const bf16*)pool, table, max_pages, \
+        page_size, talk, sink, qt_seq, qt_start, seq_off, slots, past, (bf16*)y, ldy, H, G, scale, out_scale); }
+  if (D == 64) {
+    if (hp == 8) { if (hb == 4) TM(64, 8, 4, true) else TM(64, 8, 1, true) }
+    else { if (hb == 2) TM(64, 16, 2, false) else TM(64, 16, 1, false) }
+  } else {
+    if (hp == 8) { if (hb == 4) TM(128, 8, 4, true) else TM(128, 8, 1, true) }
+    else { if (hb == 2) TM(128, 16, 2, false) else TM(128, 16, 1, false) }
+  }
+#undef TM
   LAUNCH_END();
 }
 

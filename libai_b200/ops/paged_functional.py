@@ -102,19 +102,36 @@ def conv_qkv_prepare(q, k, v, wq, wk, wv, tail, qn, kn, freq, eps: float, rb, po
 
 
 # --------------------------------------------------------------------------------------------------------------- attention
-PROMPT_QUERY_TILE = 8          # most queries of one sequence that a block of the prompt kernel takes
+PROMPT_QUERY_TILE = 8          # most queries of one sequence that a block of the generic prompt kernel takes
+MMA_QUERY_TILE = 16            # queries per block of the tensor-core prompt kernel
+MMA_HEAD_SIZES = (64, 128)     # head sizes (keys = values) the tensor-core prompt kernel is built for
+MMA_MAX_HEADS = 16
+
+
+def mma_eligible(q, pool, y, H: int, G: int, D: int, V: int) -> bool:
+    """bf16 prompt steps whose sizes the tensor-core kernel is built for (its shared memory must hold a tile of all heads)."""
+    smem = 2 * (2 * 32 * (G * D + 8) + 16 * (H * D + 8) + H * 16 * 40) + 4 * (H * 16 * 40 + 2 * H * 16)
+    return (q.dtype == torch.bfloat16 and D == V and D in MMA_HEAD_SIZES and H <= MMA_MAX_HEADS and smem <= 220 * 1024
+            and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and y.stride(0) % 2 == 0 and y.data_ptr() % 4 == 0)
 
 
 def talk_attention(q, pool, table, rb, y, H: int, G: int, D: int, V: int, scale: float, *, talk=None, sink=None,
-                   out_scale: float = 1.0, parts: Optional[int] = None):
+                   out_scale: float = 1.0, parts: Optional[int] = None, mma: bool = True):
     """Causal softmax attention of every packed query over the positions ``0 … its own`` of its sequence, keys and values read
     from the pages (the step's own rows have been written).  ``talk`` (fp32 ``[H, H]``): the heads' scaled scores are mixed
     before the softmax, ``s'_h = Σ_g talk[h, g] · s_g``; ``sink`` (fp32 ``[H]``): the denominator also holds ``exp(sink_h)``, an
     entry without a key or a value.  Query head h reads key/value head ``h // (H/G)``.  The result, times ``out_scale``, goes to
     ``y`` ``[tokens, H·V]``.  ``parts``: into how many parts the keys of a query tile are cut (``None`` chooses: single-token
-    steps spread every sequence over the device, prompt steps keep a tile's keys together)."""
+    steps spread every sequence over the device, prompt steps keep a tile's keys together).  bf16 prompt steps with head sizes
+    the tensor-core kernel is built for take it; ``mma=False`` keeps them on the generic kernel (fp32 inputs always are)."""
     if _native(q):
         ext = load_kv_ext()
+        if mma and not rb.single and parts in (None, 1) and mma_eligible(q, pool, y, H, G, D, V):
+            seq, start = rb.query_tiles(MMA_QUERY_TILE)
+            count_launch()
+            ext.talk_attention(q, pool, table, talk, sink, seq, start, MMA_QUERY_TILE, 32, rb.seq_off, rb.slots, rb.past, y, None, 1, H, G,
+                               D, V, float(scale), float(out_scale))
+            return y
         qt, kt = ext.talk_attention_tiles(1 if rb.single else PROMPT_QUERY_TILE, H, G, D, V)
         if qt == 0:
             raise RuntimeError(f"talk_attention: heads of {H}x{D} / {G}x{V} do not fit a block's shared memory")

@@ -547,3 +547,29 @@ def test_trace_runner_replays_steps(tmp_path):
     assert rel_err(got1, wb[5:6]) < 1e-4
     got2 = torch.from_numpy(np.fromfile(os.path.join(out, "2.f32"), dtype="<f4").reshape(-1, vocab).copy())
     assert rel_err(got2, wa[8:9]) < 1e-4
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("H,G,D", [(8, 2, 64), (8, 2, 128), (16, 4, 128), (6, 3, 64), (12, 12, 64), (5, 1, 128), (1, 1, 64)])
+def test_tensor_core_prompts_match_the_generic_kernel(H, G, D):
+    """bf16 prompt steps on the tensor-core kernel against the generic one: ragged lengths, a continued sequence (keys from
+    earlier pages), tiles that end inside a page, heads that do and do not fill the padded register arrays."""
+    torch.manual_seed(1)
+    ps = 16
+    cache = SequenceStateCache("cuda", torch.bfloat16, page_size=ps)
+    handle = cache.register("paged", channels=2 * G * D, taps=1, conv_channels=1)
+    slots = cache.allocate(3)
+    lens, past = [70, 1, 37], [0, 45, 90]
+    cache.prepare(slots, [a + b for a, b in zip(lens, past)])
+    bufs = cache.buffers(handle)
+    bufs["pool"].copy_(torch.randn(bufs["pool"].shape, device="cuda").to(torch.bfloat16))
+    talk = (torch.eye(H) + 0.3 * torch.randn(H, H)).cuda()
+    sink = torch.randn(H).cuda()
+    rb = RaggedBatch(lens, slots, past, "cuda")
+    q = (2.0 * torch.randn(sum(lens), H * D, device="cuda")).to(torch.bfloat16)
+    assert PF.mma_eligible(q, bufs["pool"], q, H, G, D, D)
+    got, want = torch.empty_like(q), torch.empty_like(q)
+    PF.talk_attention(q, bufs["pool"], bufs["table"], rb, got, H, G, D, D, D ** -0.5, talk=talk, sink=sink, out_scale=0.8)
+    PF.talk_attention(q, bufs["pool"], bufs["table"], rb, want, H, G, D, D, D ** -0.5, talk=talk, sink=sink, out_scale=0.8, mma=False)
+    assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+    assert float((got.float() - want.float()).abs().mean()) < 2e-3
