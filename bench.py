@@ -82,8 +82,8 @@ def parse_args():
     ap.add_argument("--serving", action="store_true",
                     help="instead of the training step: prefill / decode throughput of the stateful sequence-mixer model "
                          "(Bumodra) beside Llama at equal size (libai_b200/inference/serving_bench.py), one GPU")
-    ap.add_argument("--serving-model", choices=["bumodra", "nefelorn", "salizen"], default="bumodra",
-                    help="which stateful model --serving measures (Bumodra and Nefelorn beside Llama, Salizen beside Nefelorn)")
+    ap.add_argument("--serving-model", choices=["bumodra", "nefelorn", "salizen", "zubarax"], default="bumodra",
+                    help="which stateful model --serving measures (Bumodra and Nefelorn beside Llama, Salizen beside Nefelorn, Zubarax beside Salizen)")
     ap.add_argument("--serving-sizes", default="", help="comma separated names of serving_bench.SIZES (default: all)")
     ap.add_argument("--serving-batch", type=int, default=8)
     ap.add_argument("--serving-prompt", type=int, default=2048)

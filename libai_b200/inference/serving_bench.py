@@ -1,7 +1,8 @@
 """Prefill / decode throughput of the stateful models (Bumodra: delta-rule and latent-attention mixers; Nefelorn: ring-cached
 attention with chunk / kept-first window masks and mixture-of-experts feed-forwards) beside Llama at equal width, depth and
 (active) feed-forward size, and of Salizen (hyper-connection streams, linear-attention recurrences, sink-softmax window
-attention) beside Nefelorn, random weights, one GPU.  ``bench.py --serving [--serving-model nefelorn|salizen]`` prints the result
+attention) beside Nefelorn, and of Zubarax (post-norm blocks, paged attention with mixed heads beside an HGRN2 recurrence,
+input-weighted experts) beside Salizen, random weights, one GPU.  ``bench.py --serving [--serving-model nefelorn|salizen|zubarax]`` prints the result
 as one JSON line; ``--serving-kernels`` adds device times of the individual kernels of one block at the same sizes with their
 roofline fractions.
 
@@ -557,12 +558,196 @@ def kernel_table_salizen(s, batch, prompt):
         add(f"{phase}: Nefelorn router (sigmoid)", _time(lambda: KF.moe_route(hb, wr, top, 1.0), flush=flush), T * n * 2 + E * n * 2)
     return {"peaks": src, "hbm_bytes_per_s": hbm, "bf16_flops": flops, "rows": rows}
 
+# ======================================================================================================================
+# Zubarax beside Salizen
+# ======================================================================================================================
+def zubarax_config(s):
+    """The sizes of :data:`NEFELORN_SIZES`: the softmax side has Nefelorn's heads, the recurrence as many heads with half-size
+    keys (Salizen's gated linear attention), the experts Nefelorn's sizes plus a shared expert of one expert's size; the last
+    two entries run the first two blocks again."""
+    D, H = s["dim"], s["heads"]
+    moe = {"kind": "moe", "expert": {"ff": s["expert_ff"], "limit": 7.0}, "router": {"experts": s["experts"], "top": s["top"]},
+           "shared": {"ff": s["expert_ff"], "limit": 7.0}}
+    left = {"heads": H, "kv_heads": s["kv_heads"], "dim": D, "vdim": D, "conv": 4, "scale": D ** -0.5, "rot": {"dims": D // 2, "base": 1000000.0}}
+    right = {"heads": H, "dim": D // 2, "vdim": D}
+    entry = {"type": "parallel", "mlp": moe, "mixer": {"left": left, "right": right, "left_scale": 1.0, "right_scale": 0.7}}
+    layers = [json.loads(json.dumps(entry)) for _ in range(s["blocks"])]
+    for i in range(s["blocks"] // 2, s["blocks"]):
+        layers[i]["weights_of"] = i - s["blocks"] // 2
+    return dict(vocab=s["vocab"], width=s["width"], norm={"eps": 1e-6}, postln_alpha=2.0, embedding={"scale": s["width"] ** 0.5}, layers=layers)
+
+
+def salizen_full_window_config(s, prompt):
+    """Salizen with every block a parallel one (window attention beside gated linear attention) with experts, its window as long
+    as the prompt and the decoded tokens, one stream: the same work per block as Zubarax's."""
+    cfg = salizen_config(dict(s, reach=prompt + 64))
+    first = cfg["layers"][0]
+    first["mlp"] = json.loads(json.dumps(cfg["layers"][1]["mlp"]))
+    cfg["layers"] = [json.loads(json.dumps(first)) for _ in range(s["blocks"])]
+    cfg["streams"] = 1
+    return cfg
+
+
+@torch.no_grad()
+def throughput_zubarax(s, batch, prompt, new_tokens, steps, warmup):
+    from libai_b200.config import DictConfig
+    from libai_b200.layers._param import param_defaults
+    from libai_b200.models import SalizenForCausalLM, ZubaraxForCausalLM
+
+    ids = torch.randint(1, s["vocab"], (batch, prompt), generator=torch.Generator().manual_seed(0))
+    out = {}
+    for name, cls, cfg in (("zubarax", ZubaraxForCausalLM, zubarax_config(s)), ("salizen", SalizenForCausalLM, salizen_full_window_config(s, prompt))):
+        with param_defaults(dtype=torch.bfloat16, device="cuda", seed=1):
+            model = cls(DictConfig(cfg)).eval().cuda()
+        _stateful_throughput(model, name, ids, batch, new_tokens, steps, warmup, out)
+        del model
+        torch.cuda.empty_cache()
+    return out
+
+
+@torch.no_grad()
+def kernel_table_zubarax(s, batch, prompt):
+    """Device time of every kernel of a Zubarax block at these sizes (prefill rows = batch·prompt; decode rows = batch) beside the
+    like kernel of Salizen (or Nefelorn), with the bytes / FLOPs the operation needs and the fraction of the measured roofline."""
+    from libai_b200.inference.ragged import RaggedBatch
+    from libai_b200.inference.state_cache import SequenceStateCache
+    from libai_b200.layers import DynamicTanh
+    from libai_b200.layers._param import param_defaults
+    from libai_b200.ops import kv_functional as KF
+    from libai_b200.ops import lin_functional as LF
+    from libai_b200.ops import paged_functional as PF
+
+    hbm, flops, src = _peaks()
+    dev, bf = "cuda", torch.bfloat16
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    n, H, G, D = s["width"], s["heads"], s["kv_heads"], s["dim"]
+    E, top = s["experts"], s["top"]
+    C = G * 2 * D
+    rows = []
+
+    def add(name, ms, bytes_=0.0, fl=0.0):
+        ideal = max(bytes_ / hbm, fl / flops) * 1e3
+        rows.append(dict(kernel=name, ms=round(ms, 4), ideal_ms=round(ideal, 5), roofline_fraction=round(ideal / ms, 4),
+                         bound="memory" if bytes_ / hbm >= fl / flops else "tensor"))
+
+    with param_defaults(dtype=bf, device=dev, seed=2):
+        na, nb = DynamicTanh(n), DynamicTanh(n)
+    cache = SequenceStateCache(dev, bf, max_slots=batch, page_size=64)
+    handle = cache.register("paged", channels=C, taps=4, conv_channels=H * D + C)
+    slots = cache.allocate(batch)
+    cache.prepare(slots, [prompt + 1] * batch)
+    bufs = cache.buffers(handle)
+    bufs["pool"].copy_(torch.randn(bufs["pool"].shape, device=dev).to(bf))
+    talk = (torch.eye(H) + 0.1 * torch.randn(H, H)).to(dev)
+    sink = torch.zeros(H, device=dev)
+    for phase, lens, past in (("prefill", [prompt] * batch, [0] * batch), ("decode", [1] * batch, [prompt] * batch)):
+        rb = RaggedBatch(lens, slots, past, dev)
+        T = rb.tokens
+        x1, y32 = torch.randn(T, n, device=dev), torch.randn(T, n, device=dev)
+        h = torch.empty(T, n, dtype=bf, device=dev)
+        w = torch.zeros(n, dtype=bf, device=dev)
+        add(f"{phase}: post-norm residual (alpha x + y, RMS norm, fp32 residual + bf16 copy)",
+            _time(lambda: PF.postnorm_residual(x1, w, 1e-6, alpha=2.0, y=y32, h=h), flush=flush), T * n * 14)
+        add(f"{phase}: Nefelorn closing norm + residual + opening norm",
+            _time(lambda: KF.dyt_residual(x1, y32, post=na.triple(), nxt=nb.triple(), h=h), flush=flush), T * n * 14)
+        proj = torch.randn(T, H * D + C, device=dev).to(bf)
+        pq, pk, pv = proj[:, :H * D], proj[:, H * D:H * D + G * D], proj[:, H * D + G * D:]
+        cw = [torch.randn(c, 4, device=dev).to(bf) for c in (H * D, G * D, G * D)]
+        nw = torch.ones(D, dtype=bf, device=dev)
+        freq = KF.rotary_frequencies(D // 2, 1e6)[0].to(dev)
+        add(f"{phase}: convolution + head norms + rotation + page write of q, k, v",
+            _time(lambda: PF.conv_qkv_prepare(pq, pk, pv, cw[0], cw[1], cw[2], bufs["tail"], nw, nw, freq, 1e-6, rb, bufs["pool"], bufs["table"], H, G, D, D),
+                  flush=flush), T * (H * D + C) * 4)
+        q = torch.randn(T, H * D, device=dev).to(bf)
+        kv = torch.randn(T, C, device=dev).to(bf)
+        R = prompt + 64
+        ring = torch.randn(batch, R, C, device=dev).to(bf)
+        first = torch.zeros(batch, 0, C, dtype=bf, device=dev)
+
+        def salizen_prepare():
+            KF.qk_prepare(q, kv[:, :G * D], None, None, freq, 1.0, rb, H, G, D, 1e-6, False, False)
+            KF.kv_write(ring, first, kv[:, :G * D], kv[:, G * D:], rb)
+
+        add(f"{phase}: Salizen rotation of q, k + ring write (two kernels, no convolution, no norms)", _time(salizen_prepare, flush=flush), T * (H * D * 4 + C * 6))
+        yb = torch.empty(T, H * D, dtype=bf, device=dev)
+        if phase == "prefill":
+            pairs = prompt * (prompt + 1) // 2 * batch
+            fl = pairs * H * D * 4.0
+            add("prefill: attention over the pages with mixed heads and sink (mma.m16n8k16, mix on the fp32 pipe)",
+                _time(lambda: PF.talk_attention(q, bufs["pool"], bufs["table"], rb, yb, H, G, D, D, D ** -0.5, talk=talk, sink=sink), flush=flush),
+                T * H * D * 4 + T * C * 2, fl)
+            rows[-1]["fp32_mix_fma"] = pairs * H * H * 1.0
+            ext = rb.kv_ext([(R, 0, 0)])
+            add("prefill: Salizen window attention with sink, window = prompt (mma.m16n8k16)",
+                _time(lambda: KF.masked_attention(q, kv[:, :G * D], kv[:, G * D:], ext, None, rb, yb, H, G, D, D, R, 0, 0, D ** -0.5, sink=True), flush=flush),
+                T * H * D * 4 + T * C * 2, fl)
+        else:
+            add("decode: attention over the pages with mixed heads and sink (keys in parts + merge)",
+                _time(lambda: PF.talk_attention(q, bufs["pool"], bufs["table"], rb, yb, H, G, D, D, D ** -0.5, talk=talk, sink=sink), flush=flush),
+                batch * (prompt + 1) * C * 2)
+            add("decode: Salizen grouped ring attention with sink, window = prompt",
+                _time(lambda: KF.ring_attention(q, ring, first, None, rb, yb, H, G, D, D, R, 0, 0, D ** -0.5, sink=True), flush=flush),
+                batch * (prompt + 1) * C * 2)
+        Dg = D // 2
+        qg, kg, v2 = (torch.randn(T, H * c, device=dev).to(bf) for c in (Dg, Dg, D))
+        z, zb, low = torch.randn(T, H * Dg, device=dev), torch.randn(H * Dg, device=dev) + 2.0, torch.rand(H * Dg, device=dev) * 0.9
+        Sg = torch.zeros(batch, H, Dg, D, device=dev)
+        state_bytes = batch * H * Dg * D * 4 * (2 if phase == "decode" else 1)
+        add(f"{phase}: decay scan, bounded forget gate that also writes (state {Dg} x {D})",
+            _time(lambda: LF.decay_scan(qg, None, v2, Sg, rb, z=z, zb=zb, lower=low, act=LF.ACT_Q), flush=flush), T * H * (Dg * 6 + D * 6) + state_bytes)
+        add(f"{phase}: Salizen decay scan, decay logits per key channel (state {Dg} x {D})",
+            _time(lambda: LF.decay_scan(qg, kg, v2, Sg, rb, z=z, zb=zb, tau=8.0, q_scale=Dg ** -0.5), flush=flush), T * H * (Dg * 8 + D * 6) + state_bytes)
+        o = torch.randn(T, H * D, device=dev)
+        gate = torch.randn(T, H * D, device=dev).to(bf)
+        nw2 = torch.ones(D, dtype=bf, device=dev)
+        add(f"{phase}: RMS norm per head of the read-out (no gate)", _time(lambda: LF.gated_norm(o, None, nw2, 1e-6, LF.GATE_NONE, yb, H, D, per_head=True), flush=flush), T * H * D * 6)
+        add(f"{phase}: Salizen gated RMS norm per head", _time(lambda: LF.gated_norm(o, gate, nw2, 1e-6, LF.GATE_SILU, yb, H, D, per_head=True), flush=flush), T * H * D * 8)
+        hb = torch.randn(T, n, device=dev).to(bf)
+        wr = torch.randn(E, n, device=dev).to(bf)
+        add(f"{phase}: router (sigmoid scores as they are, top-{top} of {E})", _time(lambda: KF.moe_route(hb, wr, top, 1.0, mode=KF.ROUTE_SIGMOID_RAW), flush=flush), T * n * 2 + E * n * 2)
+        add(f"{phase}: Nefelorn router (sigmoid, normalised)", _time(lambda: KF.moe_route(hb, wr, top, 1.0), flush=flush), T * n * 2 + E * n * 2)
+        if phase == "prefill":
+            ff = s["expert_ff"]
+            gu = torch.randn(T * top, 2 * ff, device=dev).to(bf)
+            a = torch.empty(T * top, ff, dtype=bf, device=dev)
+            add("prefill: clamped gated activation of the experts", _time(lambda: KF.act_rows(gu, a, KF.ACTS["swish_clamp"], gated=True, limit=7.0), flush=flush), T * top * ff * 6)
+            add("prefill: Nefelorn gated SiLU activation", _time(lambda: KF.act_rows(gu, a, KF.ACTS["silu"], gated=True), flush=flush), T * top * ff * 6)
+            idx, wts = KF.moe_route(hb, wr, top, 1.0, mode=KF.ROUTE_SIGMOID_RAW)
+            P = T * top
+            rows_p = (P + E * 127 + 127) // 128 * 128
+            xs = torch.empty(rows_p, n, dtype=bf, device=dev)
+            meta = torch.empty(2 * E + 1 + rows_p // 128, dtype=torch.int32, device=dev)
+            pos = torch.empty(T, top, dtype=torch.int32, device=dev)
+            counts = torch.bincount(idx.reshape(-1).long(), minlength=E).int()
+            from libai_b200.ops import load_kv_ext
+
+            def sort(wv):
+                load_kv_ext().moe_sort(hb, idx, counts, meta[: E + 1], meta[E + 1: 2 * E + 1], pos, xs, 128, meta[2 * E + 1:], wv)
+
+            add("prefill: rows sorted by expert, scaled by their routing weight", _time(lambda: sort(wts), flush=flush), P * n * 4)
+            add("prefill: Nefelorn rows sorted by expert (copied)", _time(lambda: sort(None), flush=flush), P * n * 4)
+    return {"peaks": src, "hbm_bytes_per_s": hbm, "bf16_flops": flops, "rows": rows}
+
 
 def main(args):
     assert torch.cuda.is_available(), "the serving bench needs a GPU"
     from libai_b200 import ops
 
     ops.reset_launch_count()
+    if getattr(args, "serving_model", "bumodra") == "zubarax":
+        result = {"metric": "prefill / decode tokens per second, Zubarax beside Salizen (window = prompt, one stream) at equal width, depth, heads and expert sizes",
+                  "dtype": "bf16", "data": "synthetic tokens, random-init weights", "n_gpus": 1, "sizes": {}}
+        for name in (args.serving_sizes.split(",") if args.serving_sizes else list(NEFELORN_SIZES)):
+            s = NEFELORN_SIZES[name]
+            r = throughput_zubarax(s, args.serving_batch, args.serving_prompt, new_tokens=max(args.steps, 8),
+                                   steps=max(args.steps // 2, 3), warmup=max(args.warmup, 3))
+            if args.serving_kernels:
+                r["kernels"] = kernel_table_zubarax(s, args.serving_batch, args.serving_prompt)
+            result["sizes"][name] = {"config": dict(s), "batch": args.serving_batch, "prompt": args.serving_prompt, **r}
+            torch.cuda.empty_cache()
+        result["gpu_launches"] = ops.launch_count()
+        print(json.dumps(result))
+        return
     if getattr(args, "serving_model", "bumodra") == "salizen":
         result = {"metric": "prefill / decode tokens per second, Salizen beside Nefelorn at equal width, depth, heads and active feed-forward size",
                   "dtype": "bf16", "data": "synthetic tokens, random-init weights", "n_gpus": 1, "sizes": {}}
