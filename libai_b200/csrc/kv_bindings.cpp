@@ -387,7 +387,7 @@ std::vector<int64_t> talk_attention_tiles(int64_t qt_max, int64_t H, int64_t G, 
 }
 
 void talk_attention(const Tensor& q, const Tensor& pool, const Tensor& table, const OptT& talk, const OptT& sink, const Tensor& qt_seq,
-                    const Tensor& qt_start, int64_t QT, int64_t KT, const Tensor& seq_off, const Tensor& slots, const Tensor& past, Tensor y,
+                    const OptT& qt_start, int64_t QT, int64_t KT, const Tensor& seq_off, const Tensor& slots, const Tensor& past, Tensor y,
                     const OptT& part, int64_t nparts, int64_t H, int64_t G, int64_t D, int64_t V, double scale, double out_scale) {
   rows2d(q, "talk_attention q"); rows2d(y, "talk_attention y");
   const int dtype = code(q);
@@ -402,7 +402,7 @@ void talk_attention(const Tensor& q, const Tensor& pool, const Tensor& table, co
     TORCH_CHECK(dtype == 1 && nparts == 1, "talk_attention: tiles of 16 queries are the bf16 tensor-core form");
     c10::cuda::CUDAGuard guard(q.device());
     check(lbp_talk_attention_mma(q.data_ptr(), q.stride(0), pool.data_ptr(), meta(table), (int)table.size(1), (int)pool.size(1), tp, sp,
-                                 meta(qt_seq), meta(qt_start), (int)qt_seq.numel(), meta(seq_off), meta(slots), meta(past), y.data_ptr(),
+                                 meta(qt_seq), meta_opt(qt_start), (int)qt_seq.numel(), meta(seq_off), meta(slots), meta(past), y.data_ptr(),
                                  y.stride(0), (int)H, (int)G, (int)D, (int)V, (float)scale, (float)out_scale, cur_stream()),
           "talk_attention (tensor cores)");
     return;
@@ -413,7 +413,7 @@ void talk_attention(const Tensor& q, const Tensor& pool, const Tensor& table, co
   }
   c10::cuda::CUDAGuard guard(q.device());
   check(lbp_talk_attention(q.data_ptr(), q.stride(0), pool.data_ptr(), meta(table), (int)table.size(1), (int)pool.size(1), tp, sp, meta(qt_seq),
-                           meta(qt_start), (int)qt_seq.numel(), (int)QT, (int)KT, meta(seq_off), meta(slots), meta(past), y.data_ptr(), y.stride(0),
+                           meta_opt(qt_start), (int)qt_seq.numel(), (int)QT, (int)KT, meta(seq_off), meta(slots), meta(past), y.data_ptr(), y.stride(0),
                            pp, (int)nparts, rows, (int)H, (int)G, (int)D, (int)V, (float)scale, (float)out_scale, dtype, cur_stream()),
         "talk_attention");
 }
@@ -436,5 +436,5 @@ TORCH_LIBRARY(libai_b200_kv, m) {
   m.def("postnorm_residual(Tensor x, Tensor(a!)? xout, Tensor? y1, Tensor? y2, Tensor? pos, Tensor? cw, float alpha, Tensor w, float eps, Tensor(b!)? h) -> ()", &postnorm_residual);
   m.def("conv_qkv_prepare(Tensor q, Tensor k, Tensor v, Tensor wq, Tensor wk, Tensor wv, Tensor(a!) tail, Tensor qn, Tensor kn, Tensor freq, float eps, Tensor(b!) qout, Tensor(c!) pool, Tensor table, Tensor tok_seq, Tensor seq_off, Tensor slots, Tensor past, int H, int G, int D, int V) -> ()", &conv_qkv_prepare);
   m.def("talk_attention_tiles(int qt_max, int H, int G, int D, int V) -> int[]", &talk_attention_tiles);
-  m.def("talk_attention(Tensor q, Tensor pool, Tensor table, Tensor? talk, Tensor? sink, Tensor qt_seq, Tensor qt_start, int QT, int KT, Tensor seq_off, Tensor slots, Tensor past, Tensor(a!) y, Tensor(b!)? part, int nparts, int H, int G, int D, int V, float scale, float out_scale) -> ()", &talk_attention);
+  m.def("talk_attention(Tensor q, Tensor pool, Tensor table, Tensor? talk, Tensor? sink, Tensor qt_seq, Tensor? qt_start, int QT, int KT, Tensor seq_off, Tensor slots, Tensor past, Tensor(a!) y, Tensor(b!)? part, int nparts, int H, int G, int D, int V, float scale, float out_scale) -> ()", &talk_attention);
 }

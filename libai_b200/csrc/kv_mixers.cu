@@ -1023,7 +1023,17 @@ __global__ void moe_scatter_kernel(const T* __restrict__ h, long ldh, const int*
   constexpr int PER = 16 / sizeof(T);
   if (wts) {
     const float wp = wts[pair];
-    for (int i = threadIdx.x; i < n; i += blockDim.x) stf(dst + i, wp * ldf(src + i));
+    if (sizeof(T) == 2 && n % 8 == 0 && ldh % 8 == 0 && ((uintptr_t)h & 15) == 0 && ((uintptr_t)xs & 15) == 0) {
+      for (int i = threadIdx.x; i < n / 8; i += blockDim.x) {            // eight bf16 channels per 16-byte access
+        uint4 raw = reinterpret_cast<const uint4*>(src)[i];
+        __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(p2[e]); p2[e] = __floats2bfloat162_rn(wp * f.x, wp * f.y); }
+        reinterpret_cast<uint4*>(dst)[i] = raw;
+      }
+    } else {
+      for (int i = threadIdx.x; i < n; i += blockDim.x) stf(dst + i, wp * ldf(src + i));
+    }
   } else if (n % PER == 0 && ldh % PER == 0 && ((uintptr_t)h & 15) == 0 && ((uintptr_t)xs & 15) == 0) {
     for (int i = threadIdx.x; i < n / PER; i += blockDim.x)
       reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];

@@ -95,7 +95,29 @@ __global__ void postnorm_residual_kernel(const float* xin, float* xout, const Ty
 // qout, keys and values into the sequence's page row.  The tails are rewritten by a second kernel (the first tokens of a step
 // read what the last ones would overwrite).
 // ------------------------------------------------------------------------------------------------------------------
-template <typename T>
+template <typename T, int VEC> struct VecLd;
+template <typename T> struct VecLd<T, 1> { static __device__ __forceinline__ void ld(const T* p, float (&f)[1]) { f[0] = ldf(p); } };
+template <> struct VecLd<float, 4> {
+  static __device__ __forceinline__ void ld(const float* p, float (&f)[4]) { const float4 a = *reinterpret_cast<const float4*>(p); f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; }
+};
+template <> struct VecLd<bf16, 4> {
+  static __device__ __forceinline__ void ld(const bf16* p, float (&f)[4]) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    f[0] = __low2float(h2[0]); f[1] = __high2float(h2[0]); f[2] = __low2float(h2[1]); f[3] = __high2float(h2[1]);
+  }
+};
+
+__device__ __forceinline__ void st4v(float* p, float a, float b, float c, float d) { *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d); }
+__device__ __forceinline__ void st4v(bf16* p, float a, float b, float c, float d) {
+  uint2 o;
+  __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&o);
+  h2[0] = __floats2bfloat162_rn(a, b); h2[1] = __floats2bfloat162_rn(c, d);
+  *reinterpret_cast<uint2*>(p) = o;
+}
+
+// VEC consecutive channels per lane (4: every row slice and pointer is aligned to 4 elements; 1: anything)
+template <typename T, int VEC>
 __global__ void __launch_bounds__(128)
 conv_qkv_prepare_kernel(const T* __restrict__ qin, const T* __restrict__ kin, const T* __restrict__ vin, long ld,
                         const T* __restrict__ wq, const T* __restrict__ wk, const T* __restrict__ wv, int taps,
@@ -120,38 +142,69 @@ conv_qkv_prepare_kernel(const T* __restrict__ qin, const T* __restrict__ kin, co
   const T* cw = (kind == 0 ? wq : (kind == 1 ? wk : wv)) + (long)hh * n * taps;
   const int coff = kind == 0 ? hh * D : (kind == 1 ? H * D + hh * D : H * D + G * D + hh * V);
   float ss = 0.f;
-  for (int c = lane; c < n; c += 32) {
-    float acc = 0.f;
+  const bool w4 = VEC == 4 && taps == 4 && (reinterpret_cast<uintptr_t>(cw) % (4 * sizeof(T))) == 0;
+  for (int c = lane * VEC; c < n; c += 32 * VEC) {
+    float acc[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
+    if (w4) {                                    // the four taps of a channel are one aligned load
+      float wt[VEC][4];
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) VecLd<T, VEC == 4 ? 4 : 1>::ld(cw + (long)(c + e) * 4, reinterpret_cast<float (&)[VEC == 4 ? 4 : 1]>(wt[e]));
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int lt = t - 3 + j;
+        float uv[VEC];
+        if (lt >= 0) VecLd<T, VEC>::ld(in + (long)(s0 + lt) * ld + c, uv);
+        else if (pb + lt >= 0) VecLd<T, VEC>::ld(tail + ((long)slot * 3 + (3 + lt)) * C + coff + c, uv);
+        else continue;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) acc[e] += wt[e][j] * uv[e];
+      }
+    } else
     for (int j = 0; j < taps; ++j) {
       const int lt = t - R + j;
-      float uv = 0.f;
-      if (lt >= 0) uv = ldf(in + (long)(s0 + lt) * ld + c);
-      else if (pb + lt >= 0) uv = ldf(tail + ((long)slot * R + (R + lt)) * C + coff + c);
-      acc += ldf(cw + (long)c * taps + j) * uv;
+      float uv[VEC];
+      if (lt >= 0) VecLd<T, VEC>::ld(in + (long)(s0 + lt) * ld + c, uv);
+      else if (pb + lt >= 0) VecLd<T, VEC>::ld(tail + ((long)slot * R + (R + lt)) * C + coff + c, uv);
+      else continue;
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) acc[e] += ldf(cw + (long)(c + e) * taps + j) * uv[e];
     }
-    buf[c] = acc;
-    ss += acc * acc;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) { buf[c + e] = acc[e]; ss += acc[e] * acc[e]; }
   }
   ss = warp_sum(ss);
   const float r = 1.f / sqrtf(ss / (float)n + eps);
   __syncwarp();
   T* krow = pool + ((long)table[(long)slot * max_pages + p / page_size] * page_size + p % page_size) * (long)(G * D + G * V);
   if (kind == 2) {
-    for (int c = lane; c < n; c += 32) stf(krow + G * D + hh * V + c, buf[c] * r);
+    T* dv = krow + G * D + hh * V;
+    if (VEC == 4 && (reinterpret_cast<uintptr_t>(dv) % (4 * sizeof(T))) == 0) {
+      for (int c = lane * 4; c < n; c += 128) st4v(dv + c, buf[c] * r, buf[c + 1] * r, buf[c + 2] * r, buf[c + 3] * r);
+    } else {
+      for (int c = lane; c < n; c += 32) stf(dv + c, buf[c] * r);
+    }
     return;
   }
   const T* nw = kind == 0 ? qn : kn;
   T* dst = kind == 0 ? qout + tok * ldqo + hh * D : krow + hh * D;
-  for (int c = lane; c < n; c += 32) {
-    float o = buf[c] * r * ldf(nw + c);
-    if (c < 2 * half) {
-      const int i = c < half ? c : c - half;
-      const float ang = (float)p * freq[i];
-      const float cs = cosf(ang), sn = sinf(ang);
-      if (c < half) o = o * cs - buf[c + half] * r * ldf(nw + c + half) * sn;
-      else o = o * cs + buf[c - half] * r * ldf(nw + c - half) * sn;
+  int plain = 2 * half;                           // first channel that is stored by the scalar loop's pass-through branch
+  if (VEC == 4 && half % 2 == 0 && (reinterpret_cast<uintptr_t>(dst) % (4 * sizeof(T))) == 0) {
+    for (int c = 2 * half + lane * 4; c < n; c += 128)
+      st4v(dst + c, buf[c] * r * ldf(nw + c), buf[c + 1] * r * ldf(nw + c + 1), buf[c + 2] * r * ldf(nw + c + 2), buf[c + 3] * r * ldf(nw + c + 3));
+    plain = n;
+  }
+  for (int c = lane; c < (plain < n ? n : 2 * half); c += 32) {   // a lane below `half` turns its pair (c, c + half) once and writes both
+    if (c < half) {
+      const float a = buf[c] * r * ldf(nw + c), bq = buf[c + half] * r * ldf(nw + c + half);
+      float sn, cs;
+      sincosf((float)p * freq[c], &sn, &cs);
+      stf(dst + c, a * cs - bq * sn);
+      stf(dst + c + half, bq * cs + a * sn);
+    } else if (c >= 2 * half) {
+      stf(dst + c, buf[c] * r * ldf(nw + c));
     }
-    stf(dst + c, o);
   }
 }
 
@@ -207,7 +260,7 @@ talk_attention_kernel(const T* __restrict__ q, long ldq, const T* __restrict__ p
   float* Cs = Ls + H * QT;              // [H][QT] correction of this tile
   float* Ts = Cs + H * QT;              // [H][H]
   const int tid = threadIdx.x, nth = blockDim.x, warp = tid >> 5, lane = tid & 31, nw = nth >> 5;
-  const int b = qt_seq[blockIdx.x], t0 = qt_start[blockIdx.x];
+  const int b = qt_seq[blockIdx.x], t0 = qt_start ? qt_start[blockIdx.x] : 0;
   const int s0 = seq_off[b], nq = min(QT, seq_off[b + 1] - s0 - t0), pos0 = past[b] + t0;
   const long row0 = s0 + t0;
   const long slot = slots[b];
@@ -216,6 +269,7 @@ talk_attention_kernel(const T* __restrict__ q, long ldq, const T* __restrict__ p
   len = (len + KT - 1) / KT * KT;
   const int kbeg = blockIdx.y * len, kend = min(kall, kbeg + len);
   const long C = GD + GV;
+  const bool vec8 = GD % 8 == 0 && GV % 8 == 0 && (reinterpret_cast<uintptr_t>(pool) & 15) == 0;
 
   for (int i = tid; i < QT * HD; i += nth) {
     const int qi = i / HD, c = i - qi * HD;
@@ -231,8 +285,23 @@ talk_attention_kernel(const T* __restrict__ q, long ldq, const T* __restrict__ p
       const int kp = k0 + j;
       if (kp < kend) {
         const T* rowp = pool + ((long)table[slot * max_pages + kp / page_size] * page_size + kp % page_size) * C;
-        for (int c = lane; c < GD; c += 32) Ks[j * KP + c] = ldf(rowp + c);
-        for (int c = lane; c < GV; c += 32) Vs[j * GV + c] = ldf(rowp + GD + c);
+        if (sizeof(T) == 2 && vec8) {             // eight bf16 channels per lane and load
+          for (int c = lane * 8; c < GD; c += 256) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(rowp + c);
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { Ks[j * KP + c + 2 * e] = __low2float(h2[e]); Ks[j * KP + c + 2 * e + 1] = __high2float(h2[e]); }
+          }
+          for (int c = lane * 8; c < GV; c += 256) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(rowp + GD + c);
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { Vs[j * GV + c + 2 * e] = __low2float(h2[e]); Vs[j * GV + c + 2 * e + 1] = __high2float(h2[e]); }
+          }
+        } else {
+          for (int c = lane; c < GD; c += 32) Ks[j * KP + c] = ldf(rowp + c);
+          for (int c = lane; c < GV; c += 32) Vs[j * GV + c] = ldf(rowp + GD + c);
+        }
       } else {
         for (int c = lane; c < GD; c += 32) Ks[j * KP + c] = 0.f;
         for (int c = lane; c < GV; c += 32) Vs[j * GV + c] = 0.f;
@@ -335,10 +404,13 @@ talk_attention_kernel(const T* __restrict__ q, long ldq, const T* __restrict__ p
 // Tensor-core form of the prompt tiling for bf16 with equal key and value head sizes DH (mma.m16n8k16, ldmatrix,
 // cp.async).  A block takes 16 consecutive queries of one sequence and all heads, one warp per head, 32 keys at a time:
 //   1  warp h: raw scores Q_h K^T of its head on the tensor cores, times scale, as fp32 into shared memory;
-//   2  the mix over heads on the fp32 pipe: warp w takes HB output heads and 16 / HB of the rows, lane = key, the rows of
-//      `talk` of its heads in registers, so that a loaded raw score feeds HB multiply-adds; causal mask; online softmax (the
-//      running maximum and sum of the warp's 16 (head, row) pairs live in lanes 0..15); probabilities as bf16 and the
-//      correction factors into shared memory;
+//   2  the mix over heads on the fp32 pipe: warp w takes HB output heads and 16 / HB of the rows, i.e. 16 (head, row) pairs; a
+//      lane owns one pair and one half of the 32 keys, keeps its head's row of `talk` in registers and its 16 mixed scores in
+//      registers, so that the row maximum and sum are in-lane loops plus one exchange between the two halves; causal mask;
+//      online softmax (running maximum and sum in the lane); probabilities as bf16 and the correction factors into shared
+//      memory.  With heads in groups of four (HB = 4) a lane instead owns one row, four keys and the
+//      four heads of its warp, with `talk` read from shared memory, so that a loaded raw score feeds four multiply-adds (the
+//      shared-memory loads of the mix, H per mixed score otherwise, are what bounds this phase at 16 heads);
 //   3  warp h: O_h <- O_h * correction + P_h V on the tensor cores, O in registers.
 // The key tile of the next step is fetched (cp.async) while 2 and 3 run, the value tile of this step while 1 and 2 run.
 // HP is the head count padded to 8 or 16 (the size of the register arrays); QREG keeps a head's query fragments in registers.
@@ -362,7 +434,8 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" :: "n"(N)); }
 
-constexpr int TM_Q = 16, TM_K = 32, TM_SRS = TM_K + 8;           // queries, keys per tile; row stride of the fp32 scores
+constexpr int TM_Q = 16, TM_K = 32, TM_SRS = TM_K + 1;           // queries, keys per tile; row stride of the fp32 scores (odd: rows fall into different banks)
+constexpr int TM_PRS = TM_K + 8, TM_PHS = TM_Q * TM_PRS + 8;     // row and head stride of the bf16 probabilities
 
 template <int DH, int HP, int HB, bool QREG>
 __global__ void __launch_bounds__(HP * 32, 1)
@@ -376,32 +449,37 @@ talk_attention_mma_kernel(const bf16* __restrict__ q, long ldq, const bf16* __re
   const int GD = G * DH, C = 2 * GD, rep = H / G;
   const int KRS = GD + 8;                       // bf16 elements per row of the key / value tiles
   const int QRS = H * DH + 8;
-  constexpr int PRS = TM_K + 8;
+  constexpr int PRS = TM_PRS, PHS = TM_PHS;
   bf16* Ks = reinterpret_cast<bf16*>(smraw);
   bf16* Vs = Ks + TM_K * KRS;
   bf16* Qs = Vs + TM_K * KRS;
   bf16* Ps = Qs + TM_Q * QRS;                   // [H][16][PRS]
-  float* S0 = reinterpret_cast<float*>(Ps + H * TM_Q * PRS);   // [H][16][TM_SRS]
+  float* S0 = reinterpret_cast<float*>(Ps + H * PHS);          // [H][16][TM_SRS]
   float* Cs = S0 + H * TM_Q * TM_SRS;           // [H][16] correction of this tile, then the final maximum
   float* Ls = Cs + H * TM_Q;                    // [H][16] final sum
+  float* Tt = Ls + H * TM_Q;                    // [H][H] `talk` transposed: Tt[g][h]
+  constexpr bool WIDE = HB == 4;                // phase 2 with four heads per lane
   const int tid = threadIdx.x, nth = blockDim.x, warp = tid >> 5, lane = tid & 31;
-  const int b = qt_seq[blockIdx.x], t0 = qt_start[blockIdx.x];
+  const int b = qt_seq[blockIdx.x], t0 = qt_start ? qt_start[blockIdx.x] : 0;
   const int s0 = seq_off[b], nq = min(TM_Q, seq_off[b + 1] - s0 - t0), pos0 = past[b] + t0;
   const long row0 = s0 + t0;
   const long slot = slots[b];
   const int kend = pos0 + nq;
   const int h = warp, kvh = h / rep;
 
-  auto load_rows = [&](bf16* dst, int k0, int coff) {            // 32 cache rows, columns [coff, coff + GD), 16 bytes per copy
-    const int per = GD / 8;
-    for (int i = tid; i < TM_K * per; i += nth) {
-      const int j = i / per, c = (i - j * per) * 8;
+  // 32 cache rows, columns [coff, coff + GD), 16 bytes per copy: a thread keeps its column chunk and walks the rows (the
+  // launcher makes the block a multiple of the chunks per row); a page size that is a power of two is a shift
+  const int per = GD / 8, jstep = nth / per, j0 = tid / per, cc = (tid - j0 * per) * 8;
+  const int pshift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
+  auto load_rows = [&](bf16* dst, int k0, int coff) {
+    for (int j = j0; j < TM_K; j += jstep) {
       const int kp = k0 + j;
       if (kp < kend) {
-        const bf16* rowp = pool + ((long)table[slot * max_pages + kp / page_size] * page_size + kp % page_size) * (long)C + coff;
-        cp_async16(dst + j * KRS + c, rowp + c);
+        const int pg = pshift >= 0 ? kp >> pshift : kp / page_size;
+        const bf16* rowp = pool + ((long)table[slot * max_pages + pg] * page_size + (kp - pg * page_size)) * (long)C + coff;
+        cp_async16(dst + j * KRS + cc, rowp + cc);
       } else {
-        *reinterpret_cast<uint4*>(dst + j * KRS + c) = make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(dst + j * KRS + cc) = make_uint4(0u, 0u, 0u, 0u);
       }
     }
   };
@@ -416,18 +494,16 @@ talk_attention_mma_kernel(const bf16* __restrict__ q, long ldq, const bf16* __re
       *reinterpret_cast<uint4*>(Qs + r * QRS + c) = v;
     }
   }
-  // phase-2 role of this warp: heads grp * HB .. + HB - 1, rows rs * RPW .. + RPW - 1; lane r < 16 keeps the statistics of
-  // (head grp * HB + r / RPW, row rs * RPW + r % RPW)
+  // phase-2 role of this lane: pair p = lane % 16 of the warp's 16 (head, row) pairs — head grp * HB + p / RPW, row
+  // rs * RPW + p % RPW — and the keys [16 * (lane / 16), + 16) of the tile
   const int grp = warp / HB, rs = warp % HB;
-  float Tr[HB][HP];
+  const int h2 = grp * HB + (lane & 15) / RPW, i2 = rs * RPW + (lane & 15) % RPW, half = lane >> 4;
+  float Tr[HP];
 #pragma unroll
-  for (int bb = 0; bb < HB; ++bb)
-#pragma unroll
-    for (int g = 0; g < HP; ++g) {
-      const int hh = grp * HB + bb;
-      Tr[bb][g] = (g < H && hh < H) ? (talk ? talk[hh * H + g] : (g == hh ? 1.f : 0.f)) : 0.f;
-    }
+  for (int g = 0; g < HP; ++g) Tr[g] = (g < H && h2 < H) ? (talk ? talk[h2 * H + g] : (g == h2 ? 1.f : 0.f)) : 0.f;
   float m_reg = -INFINITY, l_reg = 0.f;
+  float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY}, l4[4] = {0.f, 0.f, 0.f, 0.f};      // WIDE: per head of the group
+  if (WIDE) for (int i = tid; i < H * H; i += nth) Tt[i] = talk ? talk[(i % H) * H + i / H] : (i % H == i / H ? 1.f : 0.f);
   float o[NT][4];
 #pragma unroll
   for (int n = 0; n < NT; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
@@ -458,47 +534,99 @@ talk_attention_mma_kernel(const bf16* __restrict__ q, long ldq, const bf16* __re
         mma_bf16(c1, a, bk[2], bk[3]);
       }
       float* sr = S0 + (h * TM_Q + (lane >> 2)) * TM_SRS + np * 16 + 2 * (lane & 3);
-      *reinterpret_cast<float2*>(sr) = make_float2(c0[0] * scale, c0[1] * scale);
-      *reinterpret_cast<float2*>(sr + 8 * TM_SRS) = make_float2(c0[2] * scale, c0[3] * scale);
-      *reinterpret_cast<float2*>(sr + 8) = make_float2(c1[0] * scale, c1[1] * scale);
-      *reinterpret_cast<float2*>(sr + 8 * TM_SRS + 8) = make_float2(c1[2] * scale, c1[3] * scale);
+      sr[0] = c0[0] * scale; sr[1] = c0[1] * scale;
+      sr[8 * TM_SRS] = c0[2] * scale; sr[8 * TM_SRS + 1] = c0[3] * scale;
+      sr[8] = c1[0] * scale; sr[9] = c1[1] * scale;
+      sr[8 * TM_SRS + 8] = c1[2] * scale; sr[8 * TM_SRS + 9] = c1[3] * scale;
     }
     __syncthreads();                            // all raw scores are there; the key tile is free
     if (k0 + TM_K < kend) load_rows(Ks, k0 + TM_K, 0);
     cp_async_commit();
     // 2: mix, mask, online softmax
-    if (grp * HB < H) {
-      const int kp = k0 + lane;
-      for (int rl = 0; rl < RPW; ++rl) {
-        const int i = rs * RPW + rl;
-        float acc[HB];
+    if (WIDE) {
+      const int iw = rs * RPW + (lane >> 3), kq = lane & 7;      // row, and keys [4 kq, 4 kq + 4)
+      float acc[4][4];
 #pragma unroll
-        for (int bb = 0; bb < HB; ++bb) acc[bb] = 0.f;
+      for (int bb = 0; bb < 4; ++bb)
 #pragma unroll
-        for (int g = 0; g < HP; ++g) {
-          if (g < H) {
-            const float sv = S0[(g * TM_Q + i) * TM_SRS + lane];
+        for (int j = 0; j < 4; ++j) acc[bb][j] = 0.f;
+      const float* srow = S0 + iw * TM_SRS + 4 * kq;
+      for (int g = 0; g < H; ++g) {
+        const float4 t4 = *reinterpret_cast<const float4*>(Tt + g * H + grp * 4);
+        const float tv[4] = {t4.x, t4.y, t4.z, t4.w};
+        float sv[4];
 #pragma unroll
-            for (int bb = 0; bb < HB; ++bb) acc[bb] += Tr[bb][g] * sv;
-          }
+        for (int j = 0; j < 4; ++j) sv[j] = srow[g * TM_Q * TM_SRS + j];
+#pragma unroll
+        for (int bb = 0; bb < 4; ++bb)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[bb][j] += tv[bb] * sv[j];
+      }
+      const int last = min(kend - 1, pos0 + iw) - (k0 + 4 * kq);
+#pragma unroll
+      for (int bb = 0; bb < 4; ++bb) {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (iw >= nq || j > last) acc[bb][j] = -INFINITY;
+          mx = fmaxf(mx, acc[bb][j]);
         }
-        const bool seen = i < nq && kp < kend && kp <= pos0 + i;
 #pragma unroll
-        for (int bb = 0; bb < HB; ++bb) {
-          const int hh = grp * HB + bb, r = bb * RPW + rl;
-          const float v = seen ? acc[bb] : -INFINITY;
-          const float mx = warp_max(v);
-          const float mo = __shfl_sync(0xffffffffu, m_reg, r);
-          const float mn = fmaxf(mo, mx);
-          const float pj = mn == -INFINITY ? 0.f : expf(v - mn);
-          const float sum = warp_sum(pj);
-          const float corr = mo == -INFINITY ? 0.f : expf(mo - mn);
-          if (lane == r) { m_reg = mn; l_reg = l_reg * corr + sum; }
-          if (hh < H) {
-            Ps[(hh * TM_Q + i) * PRS + lane] = __float2bfloat16_rn(pj);
-            if (lane == 0) Cs[hh * TM_Q + i] = corr;
-          }
+        for (int mk = 1; mk < 8; mk <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, mk));
+        const float mo = m4[bb], mn = fmaxf(mo, mx);
+        float pj[4], sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { pj[j] = mn == -INFINITY ? 0.f : __expf(acc[bb][j] - mn); sum += pj[j]; }
+#pragma unroll
+        for (int mk = 1; mk < 8; mk <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, mk);
+        const float corr = mo == -INFINITY ? 0.f : __expf(mo - mn);
+        m4[bb] = mn;
+        l4[bb] = l4[bb] * corr + sum;
+        const int hh = grp * 4 + bb;
+        st4v(Ps + hh * PHS + iw * PRS + 4 * kq, pj[0], pj[1], pj[2], pj[3]);
+        if (kq == 0) Cs[hh * TM_Q + iw] = corr;
+      }
+    } else if (grp * HB < H) {
+      float acc[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+      const float* srow = S0 + i2 * TM_SRS + 16 * half;
+#pragma unroll
+      for (int g = 0; g < HP; ++g) {
+        if (g < H) {
+          const float tg = Tr[g];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) acc[j] += tg * srow[g * TM_Q * TM_SRS + j];
         }
+      }
+      const int kp0 = k0 + 16 * half;
+      const int last = min(kend - 1, pos0 + i2) - kp0;          // keys 0 .. last of this half are seen
+      float mx = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        if (i2 >= nq || j > last) acc[j] = -INFINITY;
+        mx = fmaxf(mx, acc[j]);
+      }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+      const float mo = m_reg, mn = fmaxf(mo, mx);
+      float sum = 0.f;
+      uint32_t packed[8];
+#pragma unroll
+      for (int j = 0; j < 16; j += 2) {
+        const float p0 = mn == -INFINITY ? 0.f : __expf(acc[j] - mn), p1 = mn == -INFINITY ? 0.f : __expf(acc[j + 1] - mn);
+        sum += p0 + p1;
+        const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+        packed[j / 2] = *reinterpret_cast<const uint32_t*>(&pk);
+      }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 16);
+      const float corr = mo == -INFINITY ? 0.f : __expf(mo - mn);
+      m_reg = mn;
+      l_reg = l_reg * corr + sum;
+      if (h2 < H) {
+        uint32_t* pr = reinterpret_cast<uint32_t*>(Ps + h2 * PHS + i2 * PRS + 16 * half);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) pr[j] = packed[j];
+        if (half == 0) Cs[h2 * TM_Q + i2] = corr;
       }
     }
     cp_async_wait<1>();                         // the value tile (the key tile of the next step may still be in flight)
@@ -511,7 +639,7 @@ talk_attention_mma_kernel(const bf16* __restrict__ q, long ldq, const bf16* __re
 #pragma unroll
       for (int ks = 0; ks < TM_K / 16; ++ks) {
         uint32_t a[4];
-        ldsm_x4(a, Ps + (h * TM_Q + (lane & 7) + 8 * ((lane >> 3) & 1)) * PRS + ks * 16 + 8 * (lane >> 4));
+        ldsm_x4(a, Ps + h * PHS + ((lane & 7) + 8 * ((lane >> 3) & 1)) * PRS + ks * 16 + 8 * (lane >> 4));
 #pragma unroll
         for (int n2 = 0; n2 < NT / 2; ++n2) {
           uint32_t bv[4];
@@ -524,9 +652,14 @@ talk_attention_mma_kernel(const bf16* __restrict__ q, long ldq, const bf16* __re
   }
   cp_async_wait<0>();
   __syncthreads();
-  if (grp * HB < H && lane < TM_Q) {            // the statistics go to the warps that hold O
-    const int hh = grp * HB + lane / RPW, i = rs * RPW + lane % RPW;
-    if (hh < H) { Cs[hh * TM_Q + i] = m_reg; Ls[hh * TM_Q + i] = l_reg; }
+  if (WIDE) {                                   // the statistics go to the warps that hold O
+    if ((lane & 7) == 0) {
+#pragma unroll
+      for (int bb = 0; bb < 4; ++bb) { Cs[(grp * 4 + bb) * TM_Q + rs * RPW + (lane >> 3)] = m4[bb]; Ls[(grp * 4 + bb) * TM_Q + rs * RPW + (lane >> 3)] = l4[bb]; }
+    }
+  } else if (grp * HB < H && lane < TM_Q && h2 < H) {
+    Cs[h2 * TM_Q + i2] = m_reg;
+    Ls[h2 * TM_Q + i2] = l_reg;
   }
   __syncthreads();
 #pragma unroll
@@ -609,18 +742,20 @@ int lbp_conv_qkv_prepare(const void* qin, const void* kin, const void* vin, long
   const long units = tokens * (H + 2 * G);
   const unsigned grid = (unsigned)((units + warps - 1) / warps);
   const int C = H * D + G * D + G * V;
-  if (dtype) {
-    conv_qkv_prepare_kernel<bf16><<<grid, warps * 32, smem, s>>>((const bf16*)qin, (const bf16*)kin, (const bf16*)vin, ld, (const bf16*)wq,
-        (const bf16*)wk, (const bf16*)wv, taps, (const bf16*)tail, (const bf16*)qn, (const bf16*)kn, freq, half, eps, (bf16*)qout, ldqo,
-        (bf16*)pool, table, max_pages, page_size, tok_seq, seq_off, slots, past, tokens, H, G, D, V, W);
-    if (taps > 1) conv_tail_update_kernel<bf16><<<dim3((C + 127) / 128, B), 128, 0, s>>>((const bf16*)qin, (const bf16*)kin, (const bf16*)vin,
-        ld, (bf16*)tail, taps - 1, seq_off, slots, past, H * D, G * D, G * V);
-  } else {
-    conv_qkv_prepare_kernel<float><<<grid, warps * 32, smem, s>>>((const float*)qin, (const float*)kin, (const float*)vin, ld,
-        (const float*)wq, (const float*)wk, (const float*)wv, taps, (const float*)tail, (const float*)qn, (const float*)kn, freq, half,
-        eps, (float*)qout, ldqo, (float*)pool, table, max_pages, page_size, tok_seq, seq_off, slots, past, tokens, H, G, D, V, W);
-    if (taps > 1) conv_tail_update_kernel<float><<<dim3((C + 127) / 128, B), 128, 0, s>>>((const float*)qin, (const float*)kin,
-        (const float*)vin, ld, (float*)tail, taps - 1, seq_off, slots, past, H * D, G * D, G * V);
+  const int esz = dtype ? 2 : 4;
+  const bool v4 = D % 4 == 0 && V % 4 == 0 && ld % 4 == 0 && ((uintptr_t)qin % (4 * esz)) == 0 && ((uintptr_t)kin % (4 * esz)) == 0 &&
+                  ((uintptr_t)vin % (4 * esz)) == 0 && ((uintptr_t)tail % (4 * esz)) == 0;
+#define CQ(TT, VV) conv_qkv_prepare_kernel<TT, VV><<<grid, warps * 32, smem, s>>>((const TT*)qin, (const TT*)kin, (const TT*)vin, ld, (const TT*)wq, \
+        (const TT*)wk, (const TT*)wv, taps, (const TT*)tail, (const TT*)qn, (const TT*)kn, freq, half, eps, (TT*)qout, ldqo, (TT*)pool, table, \
+        max_pages, page_size, tok_seq, seq_off, slots, past, tokens, H, G, D, V, W)
+  if (dtype) { if (v4) CQ(bf16, 4); else CQ(bf16, 1); } else { if (v4) CQ(float, 4); else CQ(float, 1); }
+#undef CQ
+  if (taps > 1) {
+    const dim3 tg((C + 127) / 128, B);
+    if (dtype) conv_tail_update_kernel<bf16><<<tg, 128, 0, s>>>((const bf16*)qin, (const bf16*)kin, (const bf16*)vin, ld, (bf16*)tail, taps - 1,
+                                                               seq_off, slots, past, H * D, G * D, G * V);
+    else conv_tail_update_kernel<float><<<tg, 128, 0, s>>>((const float*)qin, (const float*)kin, (const float*)vin, ld, (float*)tail, taps - 1,
+                                                            seq_off, slots, past, H * D, G * D, G * V);
   }
   LAUNCH_END();
 }
@@ -673,13 +808,12 @@ int lbp_talk_attention_mma(const void* q, long ldq, const void* pool, const int*
                            const float* sink, const int* qt_seq, const int* qt_start, int ntiles, const int* seq_off, const int* slots,
                            const int* past, void* y, long ldy, int H, int G, int D, int V, float scale, float out_scale, cudaStream_t s) {
   if (ntiles == 0) return 0;
-  if (D != V || (D != 64 && D != 128) || H < 1 || H > 16 || H % G != 0 || ldq % 8 != 0 || ldy % 2 != 0 ||
+  if (D != V || (D != 64 && D != 128) || H < 1 || H > 16 || H % G != 0 || ldq % 8 != 0 || ldy % 2 != 0 || (H * 32) % (G * D / 8) != 0 ||
       ((uintptr_t)q & 15) != 0 || ((uintptr_t)pool & 15) != 0 || ((uintptr_t)y & 3) != 0) return -1;
   const int hp = H <= 8 ? 8 : 16;
-  const int hb = (hp == 8 && H % 4 == 0) ? 4 : ((hp == 16 && H % 2 == 0) ? 2 : 1);
+  const int hb = H % 4 == 0 ? 4 : ((hp == 16 && H % 2 == 0) ? 2 : 1);
   const int GD = G * D;
-  const size_t smem = (size_t)2 * (2 * TM_K * (GD + 8) + TM_Q * (H * D + 8) + H * TM_Q * (TM_K + 8)) +
-                      (size_t)4 * (H * TM_Q * TM_SRS + 2 * H * TM_Q);
+  const size_t smem = (size_t)2 * (2 * TM_K * (GD + 8) + TM_Q * (H * D + 8) + H * TM_PHS) + (size_t)4 * (H * TM_Q * TM_SRS + 2 * H * TM_Q + H * H);
   if (smem > 220 * 1024) return -1;
 #define TM(DH_, HP_, HB_, QR_) { \
     cudaFuncSetAttribute(talk_attention_mma_kernel<DH_, HP_, HB_, QR_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
@@ -687,10 +821,10 @@ int lbp_talk_attention_mma(const void* q, long ldq, const void* pool, const int*
         page_size, talk, sink, qt_seq, qt_start, seq_off, slots, past, (bf16*)y, ldy, H, G, scale, out_scale); }
   if (D == 64) {
     if (hp == 8) { if (hb == 4) TM(64, 8, 4, true) else TM(64, 8, 1, true) }
-    else { if (hb == 2) TM(64, 16, 2, false) else TM(64, 16, 1, false) }
+    else { if (hb == 4) TM(64, 16, 4, false) else if (hb == 2) TM(64, 16, 2, false) else TM(64, 16, 1, false) }
   } else {
     if (hp == 8) { if (hb == 4) TM(128, 8, 4, true) else TM(128, 8, 1, true) }
-    else { if (hb == 2) TM(128, 16, 2, false) else TM(128, 16, 1, false) }
+    else { if (hb == 4) TM(128, 16, 4, false) else if (hb == 2) TM(128, 16, 2, false) else TM(128, 16, 1, false) }
   }
 #undef TM
   LAUNCH_END();

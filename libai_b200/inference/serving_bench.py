@@ -669,6 +669,12 @@ def kernel_table_zubarax(s, batch, prompt):
             KF.kv_write(ring, first, kv[:, :G * D], kv[:, G * D:], rb)
 
         add(f"{phase}: Salizen rotation of q, k + ring write (two kernels, no convolution, no norms)", _time(salizen_prepare, flush=flush), T * (H * D * 4 + C * 6))
+        from libai_b200.ops import seq_functional as SF
+
+        cw_all, tail3 = torch.cat(cw, 0), torch.zeros(batch, 3, H * D + C, dtype=bf, device=dev)
+        conv_out = torch.empty_like(proj)
+        add(f"{phase}: Bumodra short convolution of the same channels (two kernels; convolution + SiLU only)",
+            _time(lambda: SF.short_conv(proj, cw_all, tail3, rb, conv_out), flush=flush), T * (H * D + C) * 4)
         yb = torch.empty(T, H * D, dtype=bf, device=dev)
         if phase == "prefill":
             pairs = prompt * (prompt + 1) // 2 * batch

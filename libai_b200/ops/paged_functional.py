@@ -110,8 +110,9 @@ MMA_MAX_HEADS = 16
 
 def mma_eligible(q, pool, y, H: int, G: int, D: int, V: int) -> bool:
     """bf16 prompt steps whose sizes the tensor-core kernel is built for (its shared memory must hold a tile of all heads)."""
-    smem = 2 * (2 * 32 * (G * D + 8) + 16 * (H * D + 8) + H * 16 * 40) + 4 * (H * 16 * 40 + 2 * H * 16)
+    smem = 2 * (2 * 32 * (G * D + 8) + 16 * (H * D + 8) + H * (16 * 40 + 8)) + 4 * (H * 16 * 33 + 2 * H * 16 + H * H)
     return (q.dtype == torch.bfloat16 and D == V and D in MMA_HEAD_SIZES and H <= MMA_MAX_HEADS and smem <= 220 * 1024
+            and H % G == 0 and (H * 32) % (G * D // 8) == 0
             and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and y.stride(0) % 2 == 0 and y.data_ptr() % 4 == 0)
 
 
@@ -135,7 +136,9 @@ def talk_attention(q, pool, table, rb, y, H: int, G: int, D: int, V: int, scale:
         qt, kt = ext.talk_attention_tiles(1 if rb.single else PROMPT_QUERY_TILE, H, G, D, V)
         if qt == 0:
             raise RuntimeError(f"talk_attention: heads of {H}x{D} / {G}x{V} do not fit a block's shared memory")
-        seq, start = rb.query_tiles(qt)
+        # single-token steps: a tile per token, named by the step's own descriptor (nothing is built on the host, so the step
+        # can be captured in a CUDA graph)
+        seq, start = (rb.tok_seq, None) if rb.single else rb.query_tiles(qt)
         if parts is None:
             parts = max(1, min(16, -(-296 // max(1, seq.numel())))) if rb.single else 1
         part = torch.empty(q.shape[0] * parts * H * (V + 2), dtype=torch.float32, device=q.device) if parts > 1 else None
