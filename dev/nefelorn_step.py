@@ -1,4 +1,4 @@
-"""Run prefill or single-token steps of a random-weight Nefelorn (or, ``--model salizen``, Salizen) model of one of the
+"""Run prefill or single-token steps of a random-weight Nefelorn (or, ``--model salizen`` / ``--model zubarax``, Salizen / Zubarax) model of one of the
 serving-bench sizes — a small, one-model workload for a profiler (launch lists, captures of one kernel):
 
     python dev/nefelorn_step.py --size w2048 --phase prefill --batch 8 --prompt 2048 --iters 2 [--model salizen]
@@ -14,7 +14,7 @@ import torch  # noqa: E402
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--model", choices=["nefelorn", "salizen"], default="nefelorn")
+    ap.add_argument("--model", choices=["nefelorn", "salizen", "zubarax"], default="nefelorn")
     ap.add_argument("--size", default="w1024")
     ap.add_argument("--phase", choices=["prefill", "decode"], default="prefill")
     ap.add_argument("--batch", type=int, default=8)
@@ -27,11 +27,13 @@ def main():
     from libai_b200.inference import serving_bench as sb
     from libai_b200.inference.scheduler import RequestScheduler
     from libai_b200.layers._param import param_defaults
-    from libai_b200.models import NefelornForCausalLM, SalizenForCausalLM
+    from libai_b200.models import NefelornForCausalLM, SalizenForCausalLM, ZubaraxForCausalLM
 
     s = sb.NEFELORN_SIZES[a.size]
     with param_defaults(dtype=torch.bfloat16, device="cuda", seed=1):
-        if a.model == "salizen":
+        if a.model == "zubarax":
+            model = ZubaraxForCausalLM(DictConfig(sb.zubarax_config(s))).eval().cuda()
+        elif a.model == "salizen":
             model = SalizenForCausalLM(DictConfig(sb.salizen_config(s))).eval().cuda()
         else:
             model = NefelornForCausalLM(DictConfig(sb.nefelorn_config(s))).eval().cuda()
