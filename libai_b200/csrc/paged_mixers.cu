@@ -769,7 +769,7 @@ static size_t talk_smem_floats(int QT, int KT, int H, int G, int D, int V) {
 // the largest query tile (at most qt_max) and key tile that fit the block's shared memory; 0 when nothing fits
 int lbp_talk_attention_tiles(int qt_max, int H, int G, int D, int V, int* kt_out) {
   const size_t cap = 200 * 1024 / sizeof(float);
-  for (int kt = 32; kt >= 8; kt >>= 1) {
+  for (int kt = 32; kt >= 1; kt >>= 1) {
     for (int qt = qt_max; qt >= 1; qt >>= 1) {
       if (kt < 32 && qt > 2) continue;          // a short key tile only where even two queries do not fit a long one
       if (talk_smem_floats(qt, kt, H, G, D, V) <= cap) { *kt_out = kt; return qt; }
