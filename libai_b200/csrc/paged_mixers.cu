@@ -56,6 +56,69 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 // be x itself) and `h` (T) receive it when given.  y1 [rows, n] (Ty) and y2 (fp32) are optional; with `pos` [rows, top]
 // y2' = sum_k cw[r, k] * y2[pos[r, k]] (cw absent: 1), else y2' = y2[r].  One block per row; the row is staged in shared memory.
 // ------------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float4 ld4f(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 ld4f(const bf16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  return make_float4(__low2float(h2[0]), __high2float(h2[0]), __low2float(h2[1]), __high2float(h2[1]));
+}
+__device__ __forceinline__ void st4f(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void st4f(bf16* p, float4 v) {
+  uint2 o;
+  __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&o);
+  h2[0] = __floats2bfloat162_rn(v.x, v.y); h2[1] = __floats2bfloat162_rn(v.z, v.w);
+  *reinterpret_cast<uint2*>(p) = o;
+}
+
+// four channels per thread and access (every row and pointer aligned to four elements); the row stays in registers when it
+// fits (at most ITEMS quadruples per thread), so nothing is staged
+template <typename T, typename Ty, int ITEMS>
+__global__ void postnorm_residual_vec_kernel(const float* xin, float* xout, const Ty* __restrict__ y1, long ldy1, const float* __restrict__ y2,
+                                             long ldy2, const int* __restrict__ pos, const float* __restrict__ cw, int top, float alpha,
+                                             const T* __restrict__ w, float eps, T* __restrict__ h, long ldh, int n) {
+  __shared__ float red[32];
+  const long row = blockIdx.x;
+  const int quads = n / 4;
+  float4 v[ITEMS];
+  float ss = 0.f;
+#pragma unroll
+  for (int it = 0; it < ITEMS; ++it) {
+    const int i = (threadIdx.x + it * blockDim.x) * 4;
+    v[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < quads * 4) {
+      float4 a = ld4f(xin + row * n + i);
+      a.x *= alpha; a.y *= alpha; a.z *= alpha; a.w *= alpha;
+      if (y1) { const float4 b = ld4f(y1 + row * ldy1 + i); a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w; }
+      if (y2) {
+        if (pos) {
+          for (int k = 0; k < top; ++k) {
+            const float c = cw ? cw[row * top + k] : 1.f;
+            const float4 b = ld4f(y2 + (long)pos[row * top + k] * ldy2 + i);
+            a.x += c * b.x; a.y += c * b.y; a.z += c * b.z; a.w += c * b.w;
+          }
+        } else {
+          const float4 b = ld4f(y2 + row * ldy2 + i);
+          a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+        }
+      }
+      v[it] = a;
+      ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+    }
+  }
+  ss = block_sum(ss, red);
+  const float r = 1.f / sqrtf(ss / (float)n + eps);
+#pragma unroll
+  for (int it = 0; it < ITEMS; ++it) {
+    const int i = (threadIdx.x + it * blockDim.x) * 4;
+    if (i < quads * 4) {
+      const float4 ww = ld4f(w + i);
+      const float4 o = make_float4(v[it].x * r * (1.f + ww.x), v[it].y * r * (1.f + ww.y), v[it].z * r * (1.f + ww.z), v[it].w * r * (1.f + ww.w));
+      if (xout) st4f(xout + row * n + i, o);
+      if (h) st4f(h + row * ldh + i, o);
+    }
+  }
+}
+
 template <typename T, typename Ty>
 __global__ void postnorm_residual_kernel(const float* xin, float* xout, const Ty* __restrict__ y1, long ldy1, const float* __restrict__ y2,
                                          long ldy2, const int* __restrict__ pos, const float* __restrict__ cw, int top, float alpha,
@@ -718,6 +781,23 @@ int lbp_postnorm_residual(const float* xin, float* xout, const void* y1, long ld
   if (rows == 0) return 0;
   const size_t smem = (size_t)n * sizeof(float);
   if (smem > 160 * 1024) return -1;
+  const int esz = dtype ? 2 : 4, y1sz = y1dtype ? 2 : 4;
+  const bool vec = n % 4 == 0 && ((uintptr_t)xin & 15) == 0 && ((uintptr_t)xout & 15) == 0 && ((uintptr_t)w % (4 * esz)) == 0 &&
+                   (!y1 || (((uintptr_t)y1 % (4 * y1sz)) == 0 && ldy1 % 4 == 0)) && (!y2 || (((uintptr_t)y2 & 15) == 0 && ldy2 % 4 == 0)) &&
+                   (!h || (((uintptr_t)h % (4 * esz)) == 0 && ldh % 4 == 0));
+  if (vec && n / 4 <= 2048) {                   // the row in registers: one or two quadruples per thread
+    const int quads = n / 4, items = quads <= 256 ? 1 : 2;
+    int vthreads = (((quads + items - 1) / items + 31) / 32) * 32;
+    if (vthreads > 1024) vthreads = 1024;
+#define PNV(TT, TY, IT) postnorm_residual_vec_kernel<TT, TY, IT><<<(unsigned)rows, vthreads, 0, s>>>(xin, xout, (const TY*)y1, ldy1, y2, ldy2, pos, cw, top, \
+        alpha, (const TT*)w, eps, (TT*)h, ldh, n)
+#define PNV2(TT, TY) { if (items == 1) PNV(TT, TY, 1); else PNV(TT, TY, 2); }
+    if (dtype) { if (y1dtype) PNV2(bf16, bf16) else PNV2(bf16, float) }
+    else { if (y1dtype) return -1; PNV2(float, float) }
+#undef PNV2
+#undef PNV
+    LAUNCH_END();
+  }
   const int threads = n >= 2048 ? 256 : 128;
 #define PN(TT, TY) { \
     if (smem > 48 * 1024) cudaFuncSetAttribute(postnorm_residual_kernel<TT, TY>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
