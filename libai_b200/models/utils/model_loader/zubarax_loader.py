@@ -32,6 +32,13 @@ class ZubaraxLoader(ModelLoaderHuggerFace):
     def _convert_state_dict(self, sd, cfg):
         owners = [i for i, lc in enumerate(cfg["layers"]) if lc.get("weights_of") is None]
         block = {str(i): k for k, i in enumerate(owners)}
+        # an entry without a feed-forward whose second norm is in the checkpoint applies it to alpha · x alone
+        bare = [i for i in owners if not cfg["layers"][i].get("mlp") and f"l{i}.norm2" in sd]
+        if bare:
+            layers = [dict(lc) for lc in cfg["layers"]]
+            for i in bare:
+                layers[i]["bare_norm2"] = True
+            self._update_cfg("layers", layers)
         out = collections.OrderedDict()
         experts = collections.defaultdict(dict)                # (block, matrix) -> {expert: tensor}
         shared = collections.defaultdict(dict)                 # block -> {gate | up: tensor}

@@ -72,14 +72,15 @@ class PostNormBlock(nn.Module):
     """``x ← norm1(α x + mixer(x))``, ``x ← norm2(α x + ff(x))`` on the fp32 residual ``x`` ``[rows, width]`` (updated in place); ``h`` is
     its copy in the compute dtype (``x`` itself in fp32), which the products read."""
 
-    def __init__(self, width, kind, mixer_cfg, mlp_cfg, alpha, eps, *, layer_idx=0):
+    def __init__(self, width, kind, mixer_cfg, mlp_cfg, alpha, eps, *, bare_norm2=False, layer_idx=0):
         super().__init__()
         self.kind, self.width, self.alpha, self.eps = kind, width, float(alpha), eps
         self.norm1 = RMSLayerNorm(width, eps=eps, layer_idx=layer_idx, zero_centered=True)
         self.mix = build_mixer(kind, width, mixer_cfg, eps, layer_idx)
-        self.mlp = self.shared = None
-        if mlp_cfg:
+        self.mlp = self.shared = self.norm2 = None
+        if mlp_cfg or bare_norm2:                              # a block without a feed-forward may still own a second norm
             self.norm2 = RMSLayerNorm(width, eps=eps, layer_idx=layer_idx, zero_centered=True)
+        if mlp_cfg:
             if mlp_cfg.get("kind", "moe") != "moe":
                 raise ValueError(f"unknown feed-forward kind {mlp_cfg.get('kind')!r}")
             r, e = mlp_cfg["router"], mlp_cfg["expert"]
@@ -123,7 +124,11 @@ class PostNormBlock(nn.Module):
         PF.postnorm_residual(x, self.norm1.weight, self.eps, alpha=self.alpha, y=o, h=hb)
         h = x if hb is None else hb
         if self.mlp is None:
-            return h
+            if self.norm2 is None:
+                return h
+            hb = self._copy(x)                                 # x ← norm2(α x): the second step with an empty sublayer
+            PF.postnorm_residual(x, self.norm2.weight, self.eps, alpha=self.alpha, h=hb)
+            return x if hb is None else hb
         d, pos, cw = self.mlp(h, graph_safe=rb.single)
         shared = self.shared(h) if self.shared is not None else None
         hb = self._copy(x)
@@ -151,7 +156,8 @@ class ZubaraxModel(nn.Module):
         self.runs = [owners.index(owner(i)) for i in range(len(layers))]
         self.owner_ids = owners                                # block k holds the tensors of entry owner_ids[k]
         self.layers = nn.ModuleList(
-            [PostNormBlock(width, layers[i]["type"], layers[i]["mixer"], layers[i].get("mlp"), postln_alpha, eps, layer_idx=i) for i in owners])
+            [PostNormBlock(width, layers[i]["type"], layers[i]["mixer"], layers[i].get("mlp"), postln_alpha, eps,
+                           bare_norm2=bool(layers[i].get("bare_norm2")), layer_idx=i) for i in owners])
         self.final_norm = RMSLayerNorm(width, eps=eps, layer_idx=-1, zero_centered=True)
 
     def register_state(self, cache: SequenceStateCache) -> List:

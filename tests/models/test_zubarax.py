@@ -416,6 +416,23 @@ def test_other_sizes(device, tmp_path, case):
         assert rel_err(got, w) < 1e-4
 
 
+@pytest.mark.parametrize("device", DEVICES)
+def test_a_second_norm_without_a_feed_forward(device, tmp_path):
+    """A checkpoint may carry the second norm of an entry that has no feed-forward: it then norms alpha · x alone, also in the
+    entry that borrows the tensors."""
+    sides = O.side_cfgs()
+    cfg = O.model_cfg([O.layer(sides, mlp=None), O.layer(sides, mlp=O.moe_cfg()), O.layer(sides, mlp=None, weights_of=0)])
+    W = O.random_weights(cfg, seed=6)
+    plain = O.forward(cfg, W, tokens(11, vocab=cfg["vocab"], seed=3))
+    W["l0.norm2"] = (0.3 * torch.randn(cfg["width"], dtype=torch.float64)).to(torch.bfloat16).double()
+    model, _ = make(tmp_path, cfg, device, weights=W)
+    p = tokens(11, vocab=cfg["vocab"], seed=3)
+    want = O.forward(cfg, W, p)
+    assert rel_err(want, plain) > 1e-2                        # the extra norm matters
+    (got,) = run_schedule(model, [p], [[6, 2, 1, 1, 1]])
+    assert rel_err(got, want) < 1e-4
+
+
 # ------------------------------------------------------------------------------------------------------------- generation
 @pytest.mark.parametrize("device", DEVICES)
 def test_greedy_generation_through_the_entry_points(device, tmp_path):
@@ -574,3 +591,24 @@ def test_tensor_core_prompts_match_the_generic_kernel(H, G, D):
     PF.talk_attention(q, bufs["pool"], bufs["table"], rb, want, H, G, D, D, D ** -0.5, talk=talk, sink=sink, out_scale=0.8, mma=False)
     assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2)
     assert float((got.float() - want.float()).abs().mean()) < 2e-3
+
+
+@pytest.mark.gpu
+def test_bf16_model_on_the_tensor_core_path(tmp_path, monkeypatch):
+    """A whole bf16 model whose head size the tensor-core prompt kernel takes: against the oracle, and against the same model
+    kept on the generic kernel."""
+    sides = O.side_cfgs(heads=4, kv_heads=2, dim=64, vdim=64, conv=3, rot_dims=32, rheads=2, rdim=16, rvdim=32)
+    cfg = O.model_cfg([O.layer(sides, mlp=None), O.layer(sides, mlp=None, weights_of=0)], width=64)
+    W = O.random_weights(cfg, seed=5)
+    model = load_pretrained(save_model(tmp_path, cfg, W), dtype=torch.bfloat16, device="cuda")
+    model.kv_page_size = 16
+    prompts = [tokens(70, seed=1), tokens(33, seed=2)]
+    want = [O.forward(cfg, W, p) for p in prompts]
+    cuts = [[60] + [1] * 10, [33]]
+    fast = run_schedule(model, prompts, cuts)
+    monkeypatch.setattr(PF, "mma_eligible", lambda *a: False)
+    slow = run_schedule(model, prompts, cuts)
+    for f, s_, w in zip(fast, slow, want):
+        assert rel_err(f, w) < 1e-1 and rel_err(s_, w) < 1e-1
+        assert rel_err(f, s_.float().cpu()) < 5e-2
+        assert not torch.equal(f, s_)                              # the two paths did run different kernels

@@ -135,6 +135,8 @@ def forward(cfg, W, tokens, residuals=None):
         x = centred_norm(alpha * x + mixer(x, W, p + "mix.", lc["mixer"], eps), W[p + "norm1"], eps)
         if lc.get("mlp"):
             x = centred_norm(alpha * x + feed_forward(x, W, p + "mlp.", lc["mlp"]), W[p + "norm2"], eps)
+        elif p + "norm2" in W:                                 # a second norm without a feed-forward norms alpha · x alone
+            x = centred_norm(alpha * x, W[p + "norm2"], eps)
         if residuals is not None:
             residuals.append(x.clone())
     return centred_norm(x, W["final.norm"], eps) @ W["embed"].T
